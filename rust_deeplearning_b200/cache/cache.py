@@ -42,7 +42,8 @@ class CacheError(RuntimeError):
 class KVRequirement:
     """Keys and values a mixer keeps per sequence.  window None: all of them.  value_dim: the size of
     a value row where it differs from a key row's (a mixer with compressed or widened values);
-    None: the same as head_dim."""
+    None: the same as head_dim; 0: no value rows are kept (a mixer whose values are part of its key
+    rows, such as one latent row per token that serves as both: `RunCache.v` is then `RunCache.k`)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
@@ -118,11 +119,13 @@ class KVGroup:
         self.pool = PagePool(n_pages)
         self.pages: Dict[int, List[int]] = {}          # slot -> page list (ring entries in order of first use)
         k_shape = (len(runs), n_pages, requirement.n_kv_heads, page_size, requirement.head_dim)
-        v_shape = k_shape[:-1] + (requirement.value_dim or requirement.head_dim,)
+        v_dim = requirement.head_dim if requirement.value_dim is None else requirement.value_dim
+        v_shape = k_shape[:-1] + (v_dim,)
         # zero-filled: kernels that copy whole pages give rows beyond a sequence's length the weight 0,
         # which needs those rows to hold finite numbers (never-written memory may not)
         self.k = torch.zeros(k_shape, dtype=dtype, device=device) if allocate else None
-        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if allocate else None
+        self.shares_values = v_dim == 0          # values are read out of the key rows
+        self.v = self.k if self.shares_values else (torch.zeros(v_shape, dtype=dtype, device=device) if allocate else None)
 
     def pages_needed(self, slot: int, length: int) -> int:
         want = min(-(-length // self.page_size), self.ring_pages)
@@ -144,7 +147,7 @@ class KVGroup:
         return out
 
     def nbytes(self):
-        return 0 if self.k is None else (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return 0 if self.k is None else (self.k.numel() + (0 if self.shares_values else self.v.numel())) * self.k.element_size()
 
 
 class StateGroup:
@@ -193,8 +196,8 @@ class Cache:
                 src = self.needs[n.reads_cache_of]
                 if not (0 <= n.reads_cache_of < e) or src.kv is None or src.reads_cache_of is not None:
                     raise CacheError(f"run {e} reads the cache of run {n.reads_cache_of}, which keeps none of its own")
-                if n.kv is not None and (n.kv.n_kv_heads, n.kv.head_dim, n.kv.value_dim or n.kv.head_dim) != \
-                        (src.kv.n_kv_heads, src.kv.head_dim, src.kv.value_dim or src.kv.head_dim):
+                vd = lambda kv: kv.head_dim if kv.value_dim is None else kv.value_dim
+                if n.kv is not None and (n.kv.n_kv_heads, n.kv.head_dim, vd(n.kv)) != (src.kv.n_kv_heads, src.kv.head_dim, vd(src.kv)):
                     raise CacheError(f"run {e} cannot read the cache of run {n.reads_cache_of}: head layout differs")
             elif n.kv is not None:
                 kv_by_req.setdefault(n.kv, []).append(e)

@@ -136,10 +136,11 @@ def registered_architectures():
 
 
 def architecture_for(raw: Dict[str, Any]) -> Architecture:
-    """Choose by `architectures[0]`, else by `model_type`; an unknown name is an error."""
+    """Choose by `architectures[0]` (or the single name under `architecture`), else by `model_type`; an
+    unknown name is an error."""
     if not isinstance(raw, dict):
         raise ConfigError("config.json must hold a JSON object")
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     if not isinstance(names, (list, tuple)):

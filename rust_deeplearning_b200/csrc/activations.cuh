@@ -4,11 +4,15 @@
 // element-wise kernel, the weight-streaming product, the tcgen05 product) goes through these.
 //   gelu_tanh(x) = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))   rustml/core/main/src/core/tensor/ops.rs:433-438
 //   silu(x) = x / (1 + exp(-x))
+// A gated feed-forward's value is gated(g, u) = act(g) * u for those two.  RDL_ACT_SWISH_LIMIT is a gated
+// form with a parameter L: g' = min(g, L), u' = clamp(u, -L, L), value g' sigmoid(1.702 g') (u' + 1).
 #pragma once
 
 #include "api.h"
 
+// codes rdl_activation takes (act(g) * u), and codes rdl_gated takes (those, and the forms with a parameter)
 static inline bool rdl_activation_known(int act) { return act == RDL_ACT_GELU_TANH || act == RDL_ACT_SILU; }
+static inline bool rdl_gated_known(int act) { return rdl_activation_known(act) || act == RDL_ACT_SWISH_LIMIT; }
 
 // exact form: library tanh and exp
 __device__ __forceinline__ float rdl_activation(float x, int act) {
@@ -29,4 +33,23 @@ __device__ __forceinline__ float rdl_activation_fast(float x, int act) {
         }
         default: return __fdividef(x, 1.0f + __expf(fminf(-x, 80.0f)));     // the divisor stays below 2^126
     }
+}
+
+// The value of a gated feed-forward from its two products; `param` is the activation's parameter (the limit of
+// RDL_ACT_SWISH_LIMIT; unused by the others).
+__device__ __forceinline__ float rdl_gated(float g, float u, int act, float param) {
+    if (act == RDL_ACT_SWISH_LIMIT) {
+        g = fminf(g, param);
+        u = fminf(fmaxf(u, -param), param);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return rdl_activation(g, act) * u;
+}
+__device__ __forceinline__ float rdl_gated_fast(float g, float u, int act, float param) {
+    if (act == RDL_ACT_SWISH_LIMIT) {
+        g = fminf(g, param);
+        u = fminf(fmaxf(u, -param), param);
+        return __fdividef(g, 1.0f + __expf(fminf(-1.702f * g, 80.0f))) * (u + 1.0f);
+    }
+    return rdl_activation_fast(g, act) * u;
 }

@@ -9,8 +9,9 @@ extern "C" {
 
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
+#define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 11
+#define RDL_ABI_VERSION 12
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -84,6 +85,7 @@ int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row_index,
                            void* y, int y_dtype, int n_rows, int hidden, void* stream);
 int rdl_gated_activation(void* out, const void* gate_up, int dtype, int activation, int n_rows, int inter, void* stream);
 int rdl_softcap_inplace(void* z_f32, long long total, float cap, void* stream);
+int rdl_scale_inplace(void* z_f32, long long total, float scale, void* stream);
 int rdl_residual_add(void* res_f32, const void* x, int x_dtype, long long total, void* stream);
 int rdl_convert_rows(void* out, int out_dtype, const void* in, int in_dtype, const int* row_index,
                      int n_rows, int width, void* stream);
@@ -159,6 +161,55 @@ int rdl_stream_rows(const float* sums, int n_sums, float eps1, const void* branc
 // when a block gives up a bounded wait.
 int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
                 int gated, int activation, float softcap, int* status, void* stream);
+
+// ---- latent attention (csrc/latent.cu) ----
+// One call per layer run and step: rotates the rotated part of every query head (in place, or into
+// q_rot_out), norms the latent, rotates the shared key part, leaves [c | kr] in latent_out and (do_write)
+// in the cache, whose rows are [kv_rank + rot_dim] wide with one key/value head.
+typedef struct {
+    int dtype, n_tokens;
+    void* rows; long long row_stride;          // the input projection's packed rows
+    int q_col, n_heads, dim, rot_dim;          // queries start at q_col: heads x [dim | rot_dim]
+    int latent_col, kv_rank;                   // [kv_rank | rot_dim] starts at latent_col; < 0: this layer has none of its own
+    const void* norm_w; int norm_w_dtype; float eps;
+    const float* cos_t; const float* sin_t;    // [positions][rot_n / 2]
+    int rot_n, interleaved;                    // dimensions that rotate (the first rot_n of the rotated part); pairing
+    const int* tok_seq; const int* tok_pos;
+    void* q_rot_out; long long q_rot_stride; int q_rot_head;   // optional: rotated query parts go to q_rot_out[t][h * q_rot_head ..]
+    void* latent_out;                          // [tokens][kv_rank + rot_dim]
+    int do_write;
+    void* cache; const int* tables; int table_width, page_size, ring_pages; const int* seq_end;
+} LatentPrepareArgs;
+int rdl_latent_prepare(const LatentPrepareArgs* a, void* stream);
+// the cache write alone, from latent_out (a write that had to wait for readers of the rows it overwrites)
+int rdl_latent_write(const LatentPrepareArgs* a, void* stream);
+// packed [Q | K | V] rows with heads padded to `pad` values, for the ordinary attention kernels
+int rdl_latent_assemble(void* out, int dtype, const void* rows, long long row_stride, int q_col, const void* kv,
+                        const void* latent, int n_tokens, int n_heads, int dim, int rot_dim, int vdim, int kv_rank,
+                        int pad, void* stream);
+// out[t, h, :vdim] = in[t, h, :vdim] * sigmoid(g[t, h]), out dense [tokens][heads * vdim]
+int rdl_gate_heads(void* out, int dtype, const void* in, long long in_stride, int in_head, const void* g, long long g_stride,
+                   int n_tokens, int n_heads, int vdim, void* stream);
+// a product per head: out[t, h, j] = sum_k w[h, j, k] x[t, h, k], optionally times sigmoid(gate[t, h])
+typedef struct {
+    int dtype, n_tokens, n_heads, n_out, k;
+    const void* x; long long x_stride; int x_head;
+    const void* w;                             // [heads][n_out][k]
+    void* out; long long out_stride; int out_head;
+    const void* gate; long long gate_stride;   // optional
+} HeadsLinearArgs;
+int rdl_heads_linear(const HeadsLinearArgs* a, void* stream);
+
+// ---- routed feed-forward (csrc/moe.cu) ----
+// sel[t, k], sel_w[t, k]: the `top` experts of row t by softmax score + correction, and their softmax scores
+int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
+                  int width, int top, int* sel, float* sel_w, void* stream);
+// mid[(t, k), :] = gated(W_gate[e] x_t, W_up[e] x_t) for e = sel[t, k] < n_real; w_gate_up [n_real][2 ff][width]
+int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, const int* sel, int n_rows, int top, int n_real,
+                    int ff, int width, int activation, float act_param, void* stream);
+// out[t, :] = sum_k sel_w[t, k] (e_k < n_real ? W_down[e_k] mid[(t, k), :] : x[t, :]); w_down [n_real][width][ff]
+int rdl_moe_down_combine(void* out, int dtype, const void* mid, const void* x, const void* w_down, const int* sel,
+                         const float* sel_w, int n_rows, int top, int n_real, int ff, int width, void* stream);
 
 // sampling over float logits [rows, vocab]
 typedef struct {

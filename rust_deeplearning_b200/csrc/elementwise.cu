@@ -366,6 +366,19 @@ extern "C" int rdl_softcap_inplace(void* z_f32, long long total, float cap, void
     return 0;
 }
 
+__global__ void scale_kernel(float* __restrict__ z, long long total, float scale) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) z[i] *= scale;
+}
+
+extern "C" int rdl_scale_inplace(void* z_f32, long long total, float scale, void* stream) {
+    RDL_REQUIRE(total >= 0, "scale: bad size");
+    if (total == 0) return 0;
+    const long long blocks = (total + 255) / 256;
+    scale_kernel<<<(unsigned)(blocks > rdl_sm_count() * 16 ? rdl_sm_count() * 16 : blocks), 256, 0, (cudaStream_t)stream>>>((float*)z_f32, total, scale);
+    RDL_CHECK_LAUNCH("scale");
+    return 0;
+}
+
 __global__ void residual_add_kernel(float* __restrict__ res, const void* __restrict__ x, int dtype, long long total) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
         res[i] += rdl_load(x, i, dtype);

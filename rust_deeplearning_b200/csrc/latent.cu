@@ -1,0 +1,264 @@
+// Kernels of the latent-attention mixer (keys and values compressed into one latent row per token).
+//
+// Per token the input projection leaves a packed row
+//   [ q: heads x (dim unrotated | rot_dim rotated) | latent (kv_rank) | shared rotated key part (rot_dim) | ... ].
+// What attention needs of it:
+//   c   = latent / sqrt(mean(latent^2) + eps) * w           the latent, normed in float
+//   kr  = R_p(shared key part),  q_rot <- R_p(q_rot)         R_p: rotation by the position's angles
+// and the cache keeps ONE row [c | kr] per token, shared by all heads.  The score of head h is
+//   (q_un[h] . W_uk[h] c  +  q_rot[h] . kr) * scale
+// and its value row is W_uv[h] c.  Two ways of computing that are served here:
+//   * expanded (whole prompts): k_un and v of every head come out of one product c [W_uk; W_uv]^T; rows
+//     [Q | K | V] with heads padded to a common size are packed for the ordinary attention kernels
+//     (rdl_latent_assemble);
+//   * absorbed (single tokens, the 32-bit path): q'[h] = [W_uk[h]^T q_un[h] | q_rot[h]] attends over the cached rows
+//     [c | kr] as keys and as values (one key/value head for all query heads), and head h's output is
+//     W_uv[h] applied to the first kv_rank values of what comes out (rdl_heads_linear does both per-head
+//     products; its epilogue can multiply by the output gate sigmoid(g[h])).
+// Rotation pairs: interleaved (2i, 2i+1) or half-split (i, i + n/2), over the first `rot_n` dimensions of
+// the rotated part; cos/sin come from float tables [position][rot_n / 2] (any scaling of frequencies or of
+// the magnitude is in the tables).
+#include "api.h"
+#include "common.cuh"
+#include "launch.cuh"
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void rotate_into(const T* src, T* dst, int n_rot, int total, int interleaved,
+                                            const float* c, const float* s, int tid, int nthreads) {
+    const int half = n_rot >> 1;
+    for (int i = tid; i < half; i += nthreads) {
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        const float u = to_float(src[a]), v = to_float(src[b]);
+        const float cs = c[i], sn = s[i];
+        const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+        dst[a] = from_float<T>(ru);
+        dst[b] = from_float<T>(rv);
+    }
+    if (dst != src)
+        for (int i = n_rot + tid; i < total; i += nthreads) dst[i] = src[i];
+}
+
+// One block of LP_THREADS per token, whatever the step's row count: the order of the sum of squares depends on
+// kv_rank alone.
+constexpr int LP_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(LatentPrepareArgs a) {
+    __shared__ float red[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = a.tok_pos[t];
+    if (pos < 0) return;                       // a padding row of a fixed-size batch
+    T* row = (T*)a.rows + (long long)t * a.row_stride;
+    const int half = a.rot_n >> 1;
+    const float* cs = a.cos_t + (long long)pos * half;
+    const float* sn = a.sin_t + (long long)pos * half;
+    const int hq = a.dim + a.rot_dim;
+    // queries: the rotated part of each head, in place or into the rows of the absorbed form
+    for (int h = 0; h < a.n_heads; ++h) {
+        const T* src = row + a.q_col + (long long)h * hq + a.dim;
+        T* dst = a.q_rot_out ? (T*)a.q_rot_out + (long long)t * a.q_rot_stride + (long long)h * a.q_rot_head : (T*)src;
+        rotate_into<T>(src, dst, a.rot_n, a.rot_dim, a.interleaved, cs, sn, threadIdx.x, LP_THREADS);
+    }
+    if (a.latent_col < 0) return;              // a layer that reads another layer's latent rows
+    // the latent: root mean square in float, a fixed order of additions
+    const T* lat = row + a.latent_col;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.kv_rank; i += LP_THREADS) {
+        const float v = to_float(lat[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)a.kv_rank + a.eps);
+    T* out = (T*)a.latent_out + (long long)t * (a.kv_rank + a.rot_dim);
+    for (int i = threadIdx.x; i < a.kv_rank; i += LP_THREADS)
+        out[i] = from_float<T>(to_float(lat[i]) * inv * rdl_load(a.norm_w, i, a.norm_w_dtype));
+    rotate_into<T>(lat + a.kv_rank, out + a.kv_rank, a.rot_n, a.rot_dim, a.interleaved, cs, sn, threadIdx.x, LP_THREADS);
+    if (!a.do_write) return;
+    const int seq = a.tok_seq[t];
+    // In a ring a later token of this step may land on the same row: only the last writer writes.
+    if ((long long)pos + (long long)a.ring_pages * a.page_size < (long long)a.seq_end[seq]) return;
+    __syncthreads();                           // the row [c | kr] is complete
+    const int width = a.kv_rank + a.rot_dim;
+    T* dst = (T*)a.cache + rdl_cache_offset(a.tables + (long long)seq * a.table_width, pos, a.page_size, a.ring_pages, 1, 0, width);
+    const int r = pos % a.page_size;           // chunks of a cache row are stored swizzled by its place in the page
+    for (int i = threadIdx.x; i < width; i += LP_THREADS) dst[rdl_cache_col<T>(r, i, width)] = out[i];
+}
+
+// A step's latent rows [c | kr] into the cache, as a kernel of its own (a ring group's write that had to wait
+// for the readers of the rows it overwrites).
+template <typename T>
+__global__ void latent_write_kernel(LatentPrepareArgs a) {
+    const int t = blockIdx.x;
+    const int pos = a.tok_pos[t];
+    if (pos < 0) return;
+    const int seq = a.tok_seq[t];
+    if ((long long)pos + (long long)a.ring_pages * a.page_size < (long long)a.seq_end[seq]) return;
+    const int width = a.kv_rank + a.rot_dim;
+    const T* src = (const T*)a.latent_out + (long long)t * width;
+    T* dst = (T*)a.cache + rdl_cache_offset(a.tables + (long long)seq * a.table_width, pos, a.page_size, a.ring_pages, 1, 0, width);
+    const int r = pos % a.page_size;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[rdl_cache_col<T>(r, i, width)] = src[i];
+}
+
+// Packed rows [Q | K | V] for the ordinary attention kernels, heads padded with zeros to `pad` values:
+//   Q[h] = [q_un[h] | q_rot[h] (rotated)], K[h] = [k_un[h] | kr], V[h] = v[h]
+// q from the projection's rows, k_un and v from the product c [W_uk; W_uv]^T ([tokens, H dim + H vdim]),
+// kr from the latent rows [c | kr].
+template <typename T>
+__global__ void latent_assemble_kernel(T* __restrict__ out, const T* __restrict__ rows, long long row_stride, int q_col,
+                                       const T* __restrict__ kv, const T* __restrict__ latent, int n_heads, int dim, int rot_dim,
+                                       int vdim, int kv_rank, int pad) {
+    const int t = blockIdx.x;
+    const int hq = dim + rot_dim;
+    const long long width = 3LL * n_heads * pad;
+    T* o = out + (long long)t * width;
+    const T* q = rows + (long long)t * row_stride + q_col;
+    const T* kvr = kv + (long long)t * n_heads * (dim + vdim);
+    const T* kr = latent + (long long)t * (kv_rank + rot_dim) + kv_rank;
+    const int per = n_heads * pad;
+    for (int i = threadIdx.x; i < 3 * per; i += blockDim.x) {
+        const int part = i / per, j = i - part * per, h = j / pad, e = j - h * pad;
+        T v = from_float<T>(0.f);
+        if (part == 0) {
+            if (e < hq) v = q[(long long)h * hq + e];
+        } else if (part == 1) {
+            if (e < dim) v = kvr[(long long)h * dim + e];
+            else if (e < hq) v = kr[e - dim];
+        } else {
+            if (e < vdim) v = kvr[(long long)n_heads * dim + (long long)h * vdim + e];
+        }
+        o[i] = v;
+    }
+}
+
+// out[t, h, i] = in[t, h, i] * sigmoid(g[t, h]) for i < vdim: the output gate on the heads of an attention result.
+template <typename T>
+__global__ void gate_heads_kernel(T* __restrict__ out, const T* __restrict__ in, long long in_stride, int in_head,
+                                  const T* __restrict__ g, long long g_stride, int n_heads, int vdim) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < n_heads * vdim; i += blockDim.x) {
+        const int h = i / vdim, e = i - h * vdim;
+        const float gate = 1.0f / (1.0f + expf(-to_float(g[(long long)t * g_stride + h])));
+        out[(long long)t * n_heads * vdim + i] = from_float<T>(to_float(in[(long long)t * in_stride + (long long)h * in_head + e]) * gate);
+    }
+}
+
+// out[t, h, j] = sum_k w[h, j, k] x[t, h, k]  (times sigmoid(g[t, h]) if g is given): a product per head.
+// One warp per (token, head, 32 consecutive j)?  No: a warp per (token tile, head, j) would re-read x; here a warp
+// takes one (head, j) for HL_ROWS tokens, lanes split k, so a weight row is read once for those tokens.  The sum
+// over k runs lane by lane in a fixed order and ends in a shuffle tree: it depends on k alone.
+constexpr int HL_ROWS = 8, HL_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(HL_WARPS * 32) heads_linear_kernel(HeadsLinearArgs a) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y, t0 = blockIdx.z * HL_ROWS;
+    const int j = blockIdx.x * HL_WARPS + warp;
+    if (j >= a.n_out) return;
+    const T* w = (const T*)a.w + ((long long)h * a.n_out + j) * a.k;
+    float acc[HL_ROWS];
+#pragma unroll
+    for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
+    const int rows = min(HL_ROWS, a.n_tokens - t0);
+    for (int k = lane; k < a.k; k += 32) {
+        const float wv = to_float(w[k]);
+#pragma unroll
+        for (int r = 0; r < HL_ROWS; ++r)
+            if (r < rows) acc[r] = fmaf(wv, to_float(((const T*)a.x)[(long long)(t0 + r) * a.x_stride + (long long)h * a.x_head + k]), acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < HL_ROWS; ++r) {
+        if (r >= rows) break;
+        float v = warp_sum(acc[r]);
+        if (lane == 0) {
+            if (a.gate) v *= 1.0f / (1.0f + expf(-to_float(((const T*)a.gate)[(long long)(t0 + r) * a.gate_stride + h])));
+            ((T*)a.out)[(long long)(t0 + r) * a.out_stride + (long long)h * a.out_head + j] = from_float<T>(v);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int rdl_latent_prepare(const LatentPrepareArgs* a, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(a->dtype), "latent_prepare: bad dtype %d", a->dtype);
+    RDL_REQUIRE(a->n_tokens >= 0 && a->n_heads > 0 && a->dim >= 0 && a->rot_dim > 0 && a->kv_rank > 0, "latent_prepare: bad sizes");
+    RDL_REQUIRE(a->rot_n >= 0 && a->rot_n % 2 == 0 && a->rot_n <= a->rot_dim, "latent_prepare: %d rotated dimensions do not fit a part of %d", a->rot_n, a->rot_dim);
+    RDL_REQUIRE(a->rows && a->tok_pos && (a->rot_n == 0 || (a->cos_t && a->sin_t)), "latent_prepare: missing rows, positions or tables");
+    RDL_REQUIRE(a->latent_col < 0 || (a->latent_out && a->norm_w), "latent_prepare: missing latent output or norm weight");
+    RDL_REQUIRE(!a->do_write || (a->latent_col >= 0 && a->cache && a->tables && a->tok_seq && a->seq_end && a->page_size > 0 && a->ring_pages > 0 &&
+                                 a->ring_pages <= a->table_width), "latent_prepare: cache write without storage or with bad paging");
+    if (a->n_tokens == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == RDL_BF16)
+        RDL_CHECK_EX(rdl_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(a->n_tokens), dim3(LP_THREADS), 0, st, *a), "latent_prepare");
+    else
+        RDL_CHECK_EX(rdl_launch(latent_prepare_kernel<float>, dim3(a->n_tokens), dim3(LP_THREADS), 0, st, *a), "latent_prepare");
+    return 0;
+}
+
+extern "C" int rdl_latent_write(const LatentPrepareArgs* a, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(a->dtype), "latent_write: bad dtype %d", a->dtype);
+    RDL_REQUIRE(a->latent_out && a->cache && a->tables && a->tok_seq && a->tok_pos && a->seq_end && a->page_size > 0 && a->ring_pages > 0 &&
+                a->ring_pages <= a->table_width, "latent_write: missing rows, storage or paging");
+    if (a->n_tokens == 0) return 0;
+    if (a->dtype == RDL_BF16)
+        latent_write_kernel<__nv_bfloat16><<<a->n_tokens, 128, 0, (cudaStream_t)stream>>>(*a);
+    else
+        latent_write_kernel<float><<<a->n_tokens, 128, 0, (cudaStream_t)stream>>>(*a);
+    RDL_CHECK_LAUNCH("latent_write");
+    return 0;
+}
+
+extern "C" int rdl_latent_assemble(void* out, int dtype, const void* rows, long long row_stride, int q_col, const void* kv,
+                                   const void* latent, int n_tokens, int n_heads, int dim, int rot_dim, int vdim, int kv_rank,
+                                   int pad, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(dtype), "latent_assemble: bad dtype %d", dtype);
+    RDL_REQUIRE(out && rows && kv && latent && n_heads > 0 && pad >= dim + rot_dim && pad >= vdim, "latent_assemble: bad arguments");
+    if (n_tokens == 0) return 0;
+    if (dtype == RDL_BF16)
+        latent_assemble_kernel<__nv_bfloat16><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)rows, row_stride, q_col, (const __nv_bfloat16*)kv, (const __nv_bfloat16*)latent,
+            n_heads, dim, rot_dim, vdim, kv_rank, pad);
+    else
+        latent_assemble_kernel<float><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((float*)out, (const float*)rows, row_stride, q_col,
+                                                                                   (const float*)kv, (const float*)latent, n_heads, dim,
+                                                                                   rot_dim, vdim, kv_rank, pad);
+    RDL_CHECK_LAUNCH("latent_assemble");
+    return 0;
+}
+
+extern "C" int rdl_gate_heads(void* out, int dtype, const void* in, long long in_stride, int in_head, const void* g, long long g_stride,
+                              int n_tokens, int n_heads, int vdim, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(dtype), "gate_heads: bad dtype %d", dtype);
+    RDL_REQUIRE(out && in && g && n_heads > 0 && vdim > 0 && in_head >= vdim, "gate_heads: bad arguments");
+    if (n_tokens == 0) return 0;
+    if (dtype == RDL_BF16)
+        gate_heads_kernel<__nv_bfloat16><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, in_stride, in_head,
+                                                                                      (const __nv_bfloat16*)g, g_stride, n_heads, vdim);
+    else
+        gate_heads_kernel<float><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((float*)out, (const float*)in, in_stride, in_head, (const float*)g,
+                                                                              g_stride, n_heads, vdim);
+    RDL_CHECK_LAUNCH("gate_heads");
+    return 0;
+}
+
+extern "C" int rdl_heads_linear(const HeadsLinearArgs* a, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(a->dtype), "heads_linear: bad dtype %d", a->dtype);
+    RDL_REQUIRE(a->out && a->x && a->w && a->n_heads > 0 && a->n_out > 0 && a->k > 0 && a->n_tokens >= 0, "heads_linear: bad arguments");
+    RDL_REQUIRE(a->n_heads <= 65535, "heads_linear: %d heads exceed the grid limit", a->n_heads);
+    if (a->n_tokens == 0) return 0;
+    const dim3 grid((a->n_out + HL_WARPS - 1) / HL_WARPS, a->n_heads, (a->n_tokens + HL_ROWS - 1) / HL_ROWS);
+    RDL_REQUIRE(grid.z <= 65535, "heads_linear: %d rows exceed the grid limit", a->n_tokens);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == RDL_BF16)
+        RDL_CHECK_EX(rdl_launch(heads_linear_kernel<__nv_bfloat16>, grid, dim3(HL_WARPS * 32), 0, st, *a), "heads_linear");
+    else
+        RDL_CHECK_EX(rdl_launch(heads_linear_kernel<float>, grid, dim3(HL_WARPS * 32), 0, st, *a), "heads_linear");
+    return 0;
+}

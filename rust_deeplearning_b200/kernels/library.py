@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 11
+ABI_VERSION = 12
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -206,6 +206,36 @@ class DeferredNormArgs(ctypes.Structure):
 NORM_BRANCH, NORM_DEFERRED = 1, 2
 
 
+class LatentPrepareArgs(ctypes.Structure):
+    """One layer run's latent-attention preparation (`csrc/api.h`)."""
+    _fields_ = [
+        ("dtype", ctypes.c_int), ("n_tokens", ctypes.c_int),
+        ("rows", ctypes.c_void_p), ("row_stride", ctypes.c_longlong),
+        ("q_col", ctypes.c_int), ("n_heads", ctypes.c_int), ("dim", ctypes.c_int), ("rot_dim", ctypes.c_int),
+        ("latent_col", ctypes.c_int), ("kv_rank", ctypes.c_int),
+        ("norm_w", ctypes.c_void_p), ("norm_w_dtype", ctypes.c_int), ("eps", ctypes.c_float),
+        ("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p),
+        ("rot_n", ctypes.c_int), ("interleaved", ctypes.c_int),
+        ("tok_seq", ctypes.c_void_p), ("tok_pos", ctypes.c_void_p),
+        ("q_rot_out", ctypes.c_void_p), ("q_rot_stride", ctypes.c_longlong), ("q_rot_head", ctypes.c_int),
+        ("latent_out", ctypes.c_void_p),
+        ("do_write", ctypes.c_int),
+        ("cache", ctypes.c_void_p), ("tables", ctypes.c_void_p), ("table_width", ctypes.c_int), ("page_size", ctypes.c_int),
+        ("ring_pages", ctypes.c_int), ("seq_end", ctypes.c_void_p),
+    ]
+
+
+class HeadsLinearArgs(ctypes.Structure):
+    """A product per head (`csrc/api.h`)."""
+    _fields_ = [
+        ("dtype", ctypes.c_int), ("n_tokens", ctypes.c_int), ("n_heads", ctypes.c_int), ("n_out", ctypes.c_int), ("k", ctypes.c_int),
+        ("x", ctypes.c_void_p), ("x_stride", ctypes.c_longlong), ("x_head", ctypes.c_int),
+        ("w", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("out_stride", ctypes.c_longlong), ("out_head", ctypes.c_int),
+        ("gate", ctypes.c_void_p), ("gate_stride", ctypes.c_longlong),
+    ]
+
+
 class SamplingArgs(ctypes.Structure):
     _fields_ = [("temperature", ctypes.c_float), ("top_k", ctypes.c_int), ("top_p", ctypes.c_float),
                 ("repetition_penalty", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
@@ -221,6 +251,7 @@ _SIGNATURES = {
     "rdl_norm_residual_norm": [_P, _I, _P, _P, _I, _F, _F, _P, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "rdl_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
     "rdl_softcap_inplace": [_P, _LL, _F, _P],
+    "rdl_scale_inplace": [_P, _LL, _F, _P],
     "rdl_residual_add": [_P, _P, _I, _LL, _P],
     "rdl_convert_rows": [_P, _I, _P, _I, _P, _I, _I, _P],
     "rdl_rope_cache": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
@@ -232,6 +263,14 @@ _SIGNATURES = {
     "rdl_random_normal": [_P, _I, _LL, ctypes.c_ulonglong, ctypes.c_double, _P],
     "rdl_sample": [_P, _P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],
     "rdl_upload_batch": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "rdl_latent_prepare": [ctypes.POINTER(LatentPrepareArgs), _P],
+    "rdl_latent_write": [ctypes.POINTER(LatentPrepareArgs), _P],
+    "rdl_latent_assemble": [_P, _I, _P, _LL, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "rdl_gate_heads": [_P, _I, _P, _LL, _I, _P, _LL, _I, _I, _I, _P],
+    "rdl_heads_linear": [ctypes.POINTER(HeadsLinearArgs), _P],
+    "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+    "rdl_moe_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "rdl_moe_down_combine": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
 }
 
 _lib = None

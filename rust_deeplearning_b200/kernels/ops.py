@@ -157,6 +157,13 @@ def softcap_(z: torch.Tensor, cap: float):
     return z
 
 
+def scale_(z: torch.Tensor, scale: float):
+    """In place on float32: z * scale."""
+    _need(z.dtype is torch.float32 and z.is_contiguous(), "scale_ takes a contiguous float32 tensor")
+    library.check(library.load().rdl_scale_inplace(_ptr(z), z.numel(), float(scale), _stream(z)))
+    return z
+
+
 def residual_add_(residual: torch.Tensor, x: torch.Tensor):
     _need(residual.dtype is torch.float32 and residual.is_contiguous() and x.is_contiguous()
           and residual.shape == x.shape, "residual_add_ takes a float32 residual and an addend of the same shape")
@@ -669,3 +676,193 @@ def upload_batch(dst: torch.Tensor, src_pinned: torch.Tensor, n_ints: int, fed: 
         _int32(sampled, "sampled")
     library.check(library.load().rdl_upload_batch(_ptr(dst), src_pinned.data_ptr(), n_ints, _ptr(sampled), src_at, tok_at, n_fed,
                                                   _stream(dst)))
+
+
+# ------------------------------------------------------------------------------------------
+# latent attention
+# ------------------------------------------------------------------------------------------
+
+def latent_prepare(rows: torch.Tensor, *, q_col: int, n_heads: int, dim: int, rot_dim: int, latent_col: Optional[int],
+                   kv_rank: int, norm: Optional[NormParams], cos: torch.Tensor, sin: torch.Tensor, rot_n: int,
+                   interleaved: bool, tok_seq: torch.Tensor, tok_pos: torch.Tensor, q_rot_out: Optional[torch.Tensor] = None,
+                   q_rot_col: int = 0, q_rot_head: int = 0, pages: Optional[KVPages] = None,
+                   seq_end: Optional[torch.Tensor] = None, write: bool = True) -> Optional[torch.Tensor]:
+    """The latent-attention step between the input projection and attention, on the projection's packed rows
+    [tokens, ...]: rotates the rotated part ([.., dim:dim + rot_dim] of each of the n_heads query heads from column
+    q_col) by the position's angles, in place or into `q_rot_out[t, q_rot_col + h * q_rot_head ...]`; and, if the layer
+    has a latent of its own (latent_col), norms its kv_rank values in float (norm: weight, eps; offset 0), rotates the
+    rot_dim values after them and returns the rows [c | kr] ([tokens, kv_rank + rot_dim]), which it also writes into the
+    cache (`pages.k`, rows of one head and that width) when `write`.  cos / sin: float32 [positions, rot_n / 2]."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1, "latent_prepare: packed rows [tokens, width]")
+    T = rows.shape[0]
+    a = library.LatentPrepareArgs()
+    a.dtype, a.n_tokens = _dtype_code(rows), T
+    a.rows, a.row_stride = rows.data_ptr(), rows.stride(0)
+    a.q_col, a.n_heads, a.dim, a.rot_dim = q_col, n_heads, dim, rot_dim
+    a.kv_rank = kv_rank
+    _need(rot_n % 2 == 0 and 0 <= rot_n <= rot_dim, "latent_prepare: the rotated dimensions must be even and fit the rotated part")
+    _need(cos.dtype is torch.float32 and sin.dtype is torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+          and cos.shape == sin.shape and cos.shape[1] * 2 == rot_n, "rotary tables must be float32 [positions, rot_n / 2]")
+    a.cos_t, a.sin_t, a.rot_n, a.interleaved = cos.data_ptr(), sin.data_ptr(), rot_n, int(interleaved)
+    _int32(tok_pos, "tok_pos", T)
+    _int32(tok_seq, "tok_seq", T)
+    a.tok_seq, a.tok_pos = tok_seq.data_ptr(), tok_pos.data_ptr()
+    _need(rows.shape[1] >= q_col + n_heads * (dim + rot_dim), "latent_prepare: the rows are narrower than the query heads")
+    if q_rot_out is not None:
+        _need(q_rot_out.dtype is rows.dtype and q_rot_out.dim() == 2 and q_rot_out.stride(1) == 1 and q_rot_out.shape[0] >= T
+              and q_rot_out.shape[1] >= q_rot_col + (n_heads - 1) * q_rot_head + rot_dim, "latent_prepare: bad q_rot_out")
+        a.q_rot_out = q_rot_out.data_ptr() + q_rot_col * rows.element_size()
+        a.q_rot_stride, a.q_rot_head = q_rot_out.stride(0), q_rot_head
+    latent = None
+    a.latent_col = -1
+    if latent_col is not None:
+        _need(rows.shape[1] >= latent_col + kv_rank + rot_dim, "latent_prepare: the rows are narrower than the latent")
+        _need(norm is not None and norm.weight.is_contiguous() and norm.weight.numel() == kv_rank and norm.offset == 0.0,
+              "latent_prepare: the latent's norm needs a plain weight of kv_rank values")
+        a.latent_col = latent_col
+        a.norm_w, a.norm_w_dtype, a.eps = norm.weight.data_ptr(), _dtype_code(norm.weight), float(norm.eps)
+        latent = torch.empty((T, kv_rank + rot_dim), dtype=rows.dtype, device=rows.device)
+        a.latent_out = latent.data_ptr()
+        if write and pages is not None:
+            _latent_cache_args(a, pages, seq_end, rows.dtype, kv_rank + rot_dim)
+    library.check(library.load().rdl_latent_prepare(ctypes.byref(a), _stream(rows)))
+    return latent
+
+
+def _latent_cache_args(a, pages: KVPages, seq_end, dtype, width):
+    _need(pages.k.dtype is dtype and pages.k.is_contiguous() and tuple(pages.k.shape[1:]) == (1, pages.page_size, width),
+          "latent cache storage must be [pages, 1, page_size, kv_rank + rot_dim] in the activations' dtype")
+    _int32(pages.tables, "page tables")
+    _int32(seq_end, "seq_end")
+    a.do_write = 1
+    a.cache, a.tables, a.table_width = pages.k.data_ptr(), pages.tables.data_ptr(), pages.tables.shape[1]
+    a.page_size, a.ring_pages, a.seq_end = pages.page_size, pages.ring_pages, seq_end.data_ptr()
+
+
+def latent_write(latent: torch.Tensor, kv_rank: int, pages: KVPages, *, tok_seq, tok_pos, seq_end):
+    """The rows [c | kr] of a step into the cache, as a call of its own."""
+    _dense(latent, "latent rows")
+    a = library.LatentPrepareArgs()
+    a.dtype, a.n_tokens = _dtype_code(latent), latent.shape[0]
+    a.kv_rank, a.rot_dim = kv_rank, latent.shape[1] - kv_rank
+    a.latent_out = latent.data_ptr()
+    _int32(tok_pos, "tok_pos", latent.shape[0])
+    _int32(tok_seq, "tok_seq", latent.shape[0])
+    a.tok_seq, a.tok_pos = tok_seq.data_ptr(), tok_pos.data_ptr()
+    _latent_cache_args(a, pages, seq_end, latent.dtype, latent.shape[1])
+    library.check(library.load().rdl_latent_write(ctypes.byref(a), _stream(latent)))
+
+
+def latent_assemble(rows: torch.Tensor, q_col: int, kv: torch.Tensor, latent: torch.Tensor, *, n_heads: int, dim: int,
+                    rot_dim: int, vdim: int, kv_rank: int, pad: int) -> torch.Tensor:
+    """Packed rows [Q | K | V], [tokens, 3 * n_heads * pad], heads zero-padded to `pad` values: Q[h] = the projection's
+    query head (its rotated part already rotated), K[h] = [k_un[h] | kr], V[h] = v[h]; kv = c [W_uk; W_uv]^T."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1, "latent_assemble: packed rows")
+    _dense(kv, "kv"); _dense(latent, "latent rows")
+    T = rows.shape[0]
+    _need(kv.dtype is rows.dtype and latent.dtype is rows.dtype and tuple(kv.shape) == (T, n_heads * (dim + vdim))
+          and tuple(latent.shape) == (T, kv_rank + rot_dim), "latent_assemble: shapes do not fit")
+    out = torch.empty((T, 3 * n_heads * pad), dtype=rows.dtype, device=rows.device)
+    library.check(library.load().rdl_latent_assemble(_ptr(out), _dtype_code(out), _ptr(rows), rows.stride(0), q_col, _ptr(kv), _ptr(latent),
+                                                     T, n_heads, dim, rot_dim, vdim, kv_rank, pad, _stream(rows)))
+    return out
+
+
+def gate_heads(x: torch.Tensor, head_stride: int, gate: torch.Tensor, n_heads: int, vdim: int) -> torch.Tensor:
+    """[tokens, n_heads * vdim] = x[t, h * head_stride + i] * sigmoid(gate[t, h]) for i < vdim; `gate` may be a
+    column slice of wider rows."""
+    _need(x.dim() == 2 and x.stride(1) == 1 and gate.dim() == 2 and gate.stride(1) == 1 and gate.dtype is x.dtype
+          and gate.shape[1] >= n_heads and x.shape[1] >= (n_heads - 1) * head_stride + vdim, "gate_heads: shapes do not fit")
+    T = x.shape[0]
+    out = torch.empty((T, n_heads * vdim), dtype=x.dtype, device=x.device)
+    library.check(library.load().rdl_gate_heads(_ptr(out), _dtype_code(out), _ptr(x), x.stride(0), head_stride, _ptr(gate), gate.stride(0),
+                                                T, n_heads, vdim, _stream(x)))
+    return out
+
+
+def heads_linear(x: torch.Tensor, x_col: int, x_head: int, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_col: int = 0,
+                 out_head: Optional[int] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A product per head: out[t, out_col + h * out_head + j] = sum_k w[h, j, k] * x[t, x_col + h * x_head + k], optionally
+    times sigmoid(gate[t, h]).  w: [heads, n_out, k].  Without `out` the result is dense [tokens, heads * n_out]."""
+    _need(x.dim() == 2 and x.stride(1) == 1 and w.dim() == 3 and w.is_contiguous() and w.dtype is x.dtype, "heads_linear: bad operands")
+    H, n_out, k = w.shape
+    T = x.shape[0]
+    _need(x.shape[1] >= x_col + (H - 1) * x_head + k, "heads_linear: the rows are narrower than the heads")
+    if out is None:
+        out = torch.empty((T, H * n_out), dtype=x.dtype, device=x.device)
+        out_head = n_out
+    _need(out.dtype is x.dtype and out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= T
+          and out.shape[1] >= out_col + (H - 1) * out_head + n_out, "heads_linear: bad output rows")
+    a = library.HeadsLinearArgs()
+    a.dtype, a.n_tokens, a.n_heads, a.n_out, a.k = _dtype_code(x), T, H, n_out, k
+    es = x.element_size()
+    a.x, a.x_stride, a.x_head = x.data_ptr() + x_col * es, x.stride(0), x_head
+    a.w = w.data_ptr()
+    a.out, a.out_stride, a.out_head = out.data_ptr() + out_col * es, out.stride(0), out_head
+    if gate is not None:
+        _need(gate.dtype is x.dtype and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[1] >= H, "heads_linear: bad gate")
+        a.gate, a.gate_stride = gate.data_ptr(), gate.stride(0)
+    library.check(library.load().rdl_heads_linear(ctypes.byref(a), _stream(x)))
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# routed feed-forward
+# ------------------------------------------------------------------------------------------
+
+# gated forms with a parameter (`csrc/activations.cuh`): name -> code
+GATED_FORMS = dict(ACTIVATIONS, swish_limit=2)
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int):
+    """Per row: softmax over all experts of the float32 logits W_r x; the `top` experts with the largest score +
+    correction (int32 [rows, top]) and their scores without it (float32 [rows, top])."""
+    _dense(x, "x")
+    _need(w_router.dtype is torch.float32 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1], "moe_route: float32 router [experts, width]")
+    E = w_router.shape[0]
+    if correction is not None:
+        _need(correction.dtype is torch.float32 and correction.is_contiguous() and correction.numel() == E, "moe_route: float32 correction [experts]")
+    sel = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
+    sel_w = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
+    library.check(library.load().rdl_moe_route(_ptr(x), _dtype_code(x), _ptr(w_router), _ptr(correction), x.shape[0], E, x.shape[1], top,
+                                               _ptr(sel), _ptr(sel_w), _stream(x)))
+    return sel, sel_w
+
+
+MOE_PAIR_ROWS = 4096     # rows of one launch of the per-pair expert kernels (their grids hold rows x top <= 65,535)
+
+
+def moe_experts_few(x: torch.Tensor, sel: torch.Tensor, sel_w: torch.Tensor, w_gate_up: Optional[torch.Tensor],
+                    w_down: Optional[torch.Tensor], n_real: int, form: str, param: float) -> torch.Tensor:
+    """The routed experts with every (row, choice) pair streaming its expert's matrices: out[t] = sum_k sel_w[t, k] y_k,
+    y_k = W_down[e] gated(W_gate[e] x_t, W_up[e] x_t) for e = sel[t, k] < n_real, else x_t (an identity expert).
+    w_gate_up: [n_real, 2 ff, width] (an expert's gate rows, then its up rows); w_down: [n_real, width, ff]."""
+    _dense(x, "x")
+    T, width = x.shape
+    top = sel.shape[1]
+    _need(form in GATED_FORMS, f"unknown gated form '{form}', known: {sorted(GATED_FORMS)}")
+    ff = 0
+    if n_real:
+        _need(w_gate_up.dtype is x.dtype and w_down.dtype is x.dtype and w_gate_up.is_contiguous() and w_down.is_contiguous()
+              and w_gate_up.dim() == 3 and w_gate_up.shape[0] == n_real and w_gate_up.shape[2] == width and w_gate_up.shape[1] % 2 == 0
+              and tuple(w_down.shape) == (n_real, width, w_gate_up.shape[1] // 2), "moe_experts_few: expert matrices do not fit")
+        ff = w_gate_up.shape[1] // 2
+    out = torch.empty_like(x)
+    lib = library.load()
+    step = max(1, min(MOE_PAIR_ROWS, 65535 // top))
+    for r0 in range(0, T, step):
+        n = min(step, T - r0)
+        xs, ss, sw, os_ = x[r0:r0 + n], sel[r0:r0 + n], sel_w[r0:r0 + n], out[r0:r0 + n]
+        mid = None
+        if n_real:
+            mid = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
+            library.check(lib.rdl_moe_gate_up(_ptr(mid), _dtype_code(x), _ptr(xs), _ptr(w_gate_up), _ptr(ss), n, top, n_real, ff, width,
+                                              GATED_FORMS[form], float(param), _stream(x)))
+        library.check(lib.rdl_moe_down_combine(_ptr(os_), _dtype_code(x), _ptr(mid), _ptr(xs), _ptr(w_down), _ptr(ss), _ptr(sw), n, top,
+                                               n_real, max(ff, 1), width, _stream(x)))
+    return out
+
+
+def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param: float) -> torch.Tensor:
+    """The routed experts' weighted sum for every row (see `moe_experts_few` for the meaning of the arguments)."""
+    return moe_experts_few(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)

@@ -1,2 +1,2 @@
 """Parts of a model.  Importing the package registers the built-in kinds."""
-from . import attention, feed_forward, model, norm, position  # noqa: F401
+from . import attention, feed_forward, latent_attention, model, norm, position, routed_experts  # noqa: F401

@@ -41,30 +41,33 @@ register_part("embedding", "scaled_embedding",
 
 
 class LinearHead:
-    """float32 logits = soft-cap(n W^T)."""
+    """float32 logits = soft-cap(n W^T) * scale (the scale applied to the float32 result, after any soft-cap)."""
 
-    def __init__(self, weight: torch.Tensor, softcap: Optional[float]):
-        self.weight, self.softcap = weight, softcap
+    def __init__(self, weight: torch.Tensor, softcap: Optional[float], scale: float = 1.0):
+        self.weight, self.softcap, self.scale = weight, softcap, float(scale)
 
     takes_deferred_rows = True      # n goes into one product and nowhere else
 
     def forward(self, n) -> torch.Tensor:
-        return ops.linear(n, self.weight, out_dtype=torch.float32, softcap=self.softcap)
+        z = ops.linear(n, self.weight, out_dtype=torch.float32, softcap=self.softcap)
+        return ops.scale_(z, self.scale) if self.scale != 1.0 else z
 
 
 register_part("head", "linear_head",
-              lambda spec, ctx: LinearHead(ctx.tensor(spec.tensors["weight"]), spec.params.get("softcap")),
+              lambda spec, ctx: LinearHead(ctx.tensor(spec.tensors["weight"]), spec.params.get("softcap"),
+                                           spec.params.get("scale", 1.0)),
               replace=True)
 
 
 class SandwichBlock:
-    """pre-norm -> mixer -> optional post-norm -> add; pre-norm -> feed-forward -> optional post-norm -> add."""
+    """pre-norm -> mixer -> optional post-norm -> add; pre-norm -> feed-forward -> optional post-norm -> add.
+    A layer without a feed-forward (`LayerSpec.feed_forward` None) ends after the mixer's branch."""
 
     def __init__(self, mixer, feed_forward, norms: Dict[str, object], act_dtype: torch.dtype):
         self.mixer, self.feed_forward = mixer, feed_forward
         self.pre_mixer = norms["pre_mixer"]
         self.post_mixer = norms.get("post_mixer")
-        self.pre_ff = norms["pre_feed_forward"]
+        self.pre_ff = norms["pre_feed_forward"] if feed_forward is not None else None
         self.post_ff = norms.get("post_feed_forward")
         self.act_dtype = act_dtype
 
@@ -82,6 +85,12 @@ class SandwichBlock:
         m_in, m_out = getattr(mixer, "takes_deferred_rows", False), getattr(mixer, "delivers_branch", False)
         f_in, f_out = getattr(ff, "takes_deferred_rows", False), getattr(ff, "delivers_branch", False)
         after, stream.norm_after_block = stream.norm_after_block, None
+        if ff is None:
+            x = stream.normed(self.pre_mixer, self.act_dtype, deferred_ok=m_in, upcoming=after if m_out else None)
+            sink = stream.branch_sink(self.post_mixer, after) if (m_out and after is not None) else None
+            a = mixer.forward(x, batch, cache, run, sink=sink) if sink is not None else mixer.forward(x, batch, cache, run)
+            stream.add(a, self.post_mixer)
+            return
         x = stream.normed(self.pre_mixer, self.act_dtype, deferred_ok=m_in, upcoming=self.pre_ff if (m_out and f_in) else None)
         sink = stream.branch_sink(self.post_mixer, self.pre_ff) if (m_out and f_in) else None
         a = mixer.forward(x, batch, cache, run, sink=sink) if sink is not None else mixer.forward(x, batch, cache, run)
@@ -94,7 +103,7 @@ class SandwichBlock:
 
 def _build_sandwich(layer: LayerSpec, ctx: BuildContext) -> SandwichBlock:
     mixer = build_part("mixer", layer.mixer, ctx)
-    ff = build_part("feed_forward", layer.feed_forward, ctx)
+    ff = build_part("feed_forward", layer.feed_forward, ctx) if layer.feed_forward is not None else None
     norms = {role: build_part("norm", s, ctx) for role, s in layer.norms.items()}
     return SandwichBlock(mixer, ff, norms, ctx.dtype)
 
@@ -116,7 +125,7 @@ class Model:
             self.layers.append(build_block(layer, ctx))
             # parts hold what they need (fused copies or the tensors themselves)
             for p in (layer.mixer, layer.feed_forward, *layer.norms.values()):
-                for t in p.tensors.values():
+                for t in (p.tensors.values() if p is not None else ()):
                     if t.name not in keep:
                         weights.pop(t.name, None)
         self.final_norm = build_part("norm", spec.final_norm, ctx)

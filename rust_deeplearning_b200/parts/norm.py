@@ -1,8 +1,10 @@
 """Norms and the residual stream.
 
-`RMSNorm` is y = x / sqrt(mean(x^2) + eps) * (w + offset)
+`RMSNorm` is y = x / sqrt(mean(x^2) + eps) * (w + offset) * scale
 (`rustml/core/main/src/core/tensor/ops.rs:735-743`, offset in
-`rustml/nn/main/src/core/rms_norm.rs:43-50`); eps and offset are parameters.
+`rustml/nn/main/src/core/rms_norm.rs:43-50`); eps, offset and scale are parameters.  A scale other
+than 1 (a multiplier on a branch before it joins the residual stream, say) is folded into a float32
+copy of the column factors, (w + offset) * scale, once at build time: the kernels see an ordinary norm.
 
 `ResidualStream` keeps the float32 sum of the block outputs.  A block adds a branch
 with `add(branch, post_norm)` and asks for `normed(norm)`: when both norms offer
@@ -46,7 +48,10 @@ def _build_rms_norm(spec: PartSpec, ctx: BuildContext) -> RMSNorm:
     w = ctx.tensor(spec.tensors["weight"])
     if w.numel() != p["size"]:
         raise ValueError(f"rms_norm: weight of {w.numel()} values for size {p['size']}")
-    return RMSNorm(w, p["eps"], p.get("offset", 0.0))
+    offset, scale = float(p.get("offset", 0.0)), float(p.get("scale", 1.0))
+    if scale != 1.0:
+        w, offset = ((w.to(torch.float32) + offset) * scale).contiguous(), 0.0
+    return RMSNorm(w, p["eps"], offset)
 
 
 register_part("norm", "rms_norm", _build_rms_norm, replace=True)

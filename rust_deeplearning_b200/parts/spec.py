@@ -21,12 +21,13 @@ class TensorSpec:
           "vector"  - small parameter; a tensor stored in 32 bits stays 32-bit, otherwise it follows
                       the compute dtype
           "int"     - integer table, kept as int32
-    init_std: standard deviation used by the random-weights mode.
+    init_std, init_mean: standard deviation and mean used by the random-weights mode.
     """
     name: str
     shape: Tuple[int, ...]
     kind: str = "matrix"
     init_std: float = 0.02
+    init_mean: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -42,7 +43,7 @@ class LayerSpec:
     """One layer: the arrangement (`block`) and the parts it arranges."""
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]      # None: the layer has a mixer only
     norms: Dict[str, PartSpec]
 
 
@@ -76,7 +77,8 @@ class ModelSpec:
         yield self.embedding
         for layer in self.layers:
             yield layer.mixer
-            yield layer.feed_forward
+            if layer.feed_forward is not None:
+                yield layer.feed_forward
             for n in layer.norms.values():
                 yield n
         yield self.final_norm

@@ -105,8 +105,11 @@ def random_tensor(t: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") ->
         n *= int(d)
     if torch.device(device).type == "cuda":
         from ..kernels import ops
-        return ops.random_normal(tuple(t.shape), key, t.init_std, dtype, device)
-    x = torch.from_numpy(counter_random.normal(n, key, t.init_std)).reshape(tuple(t.shape))
+        x = ops.random_normal(tuple(t.shape), key, t.init_std, torch.float32 if t.init_mean else dtype, device)
+    else:
+        x = torch.from_numpy(counter_random.normal(n, key, t.init_std)).reshape(tuple(t.shape))
+    if t.init_mean:      # one float32 addition, rounded once: the same bits on the host and on the device
+        x = x.to(torch.float32) + torch.tensor(t.init_mean, dtype=torch.float32, device=x.device)
     return x.to(dtype)
 
 
