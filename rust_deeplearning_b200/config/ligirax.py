@@ -253,8 +253,8 @@ def build_spec(cfg: LigiraxConfig) -> ModelSpec:
         if layer.mlp is not None:
             f = layer.mlp
             total = f.experts + f.identity
-            ft = {"router": TensorSpec(p + "mlp.router", (total, W)),
-                  "correction": TensorSpec(p + "mlp.correction", (total,), "vector")}
+            ft = {"router": TensorSpec(p + "mlp.router", (total, W), init_std=0.5),
+                  "correction": TensorSpec(p + "mlp.correction", (total,), "vector", init_std=0.2)}
             for e in range(f.experts):
                 ft[f"gate{e}"] = TensorSpec(p + f"mlp.e{e}.gate", (f.ff, W))
                 ft[f"up{e}"] = TensorSpec(p + f"mlp.e{e}.up", (f.ff, W))
@@ -267,7 +267,7 @@ def build_spec(cfg: LigiraxConfig) -> ModelSpec:
             ignored += [p + "norm2", p + "norm2b"]      # a file may carry them; a layer without a feed-forward reads neither
         layers.append(LayerSpec("sandwich", mixer, ff, norms))
 
-    table = TensorSpec("embed", (V, W), init_std=1.0)
+    table = TensorSpec("embed", (V, W), init_std=0.5)
     spec = ModelSpec(
         architecture=ARCHITECTURE_NAME, hidden_size=W, vocab_size=V, max_positions=cfg.max_positions,
         embedding=PartSpec("scaled_embedding", {"vocab_size": V, "hidden_size": W, "scale": 1.0}, {"table": table}),
