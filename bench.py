@@ -229,6 +229,100 @@ def workload(cfg, prompt_lens, new_tokens, pk, torch, rng, seed=0):
     return out
 
 
+# ---- a second design beside its closest registered model, at equal layer sizes (--design ligirax) ----
+
+def ligirax_shape(width, heads, dim, rot_dim, vdim, kv_rank, window, experts, identity, top, ff, layers, vocab, shared_from=None):
+    """A Ligirax configuration of `layers` equal layers (the later half reading the rows of layer `shared_from` if given)."""
+    rot = {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    out = []
+    for i in range(layers):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5,
+             "rot": rot, "mask": {"size": window}}
+        if shared_from is not None and i > shared_from:
+            m["kv_from"] = shared_from
+        out.append({"type": "latent_attention", "mixer": m,
+                    "mlp": {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top}}})
+    return {"architecture": "Ligirax", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "logit_scale": 1.0,
+            "max_positions": CONTEXT, "layers": out}
+
+
+def gemma_like(width, heads, head_dim, intermediate, window, layers, vocab):
+    """The Gemma 2 configuration with the same width, head count and window, whose feed-forward is as wide as the
+    experts a Ligirax token uses."""
+    return dict(GEMMA2_2B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=heads,
+                head_dim=head_dim, intermediate_size=intermediate, vocab_size=vocab, sliding_window=window,
+                query_pre_attn_scalar=head_dim, max_position_embeddings=CONTEXT)
+
+
+DESIGN_SIZES = {
+    # name: (Ligirax arguments, the Gemma 2 arguments of equal width / heads / active feed-forward width)
+    "w1024": (dict(width=1024, heads=8, dim=64, rot_dim=64, vdim=128, kv_rank=192, window=1024, experts=16, identity=2, top=2, ff=1024,
+                   layers=4, vocab=32000, shared_from=1),
+              dict(width=1024, heads=8, head_dim=128, intermediate=2048, window=1024, layers=4, vocab=32000)),
+    "w2048": (dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=4096, experts=64, identity=2, top=6, ff=1408,
+                   layers=4, vocab=32000),
+              dict(width=2048, heads=16, head_dim=128, intermediate=8448, window=4096, layers=4, vocab=32000)),
+}
+
+
+def design_point(cfg, vocab, torch, rng, steps, warmup, prompt_len, batches):
+    """Prefill tokens/s (one prompt in one step, median of 5 after 3) and decode tokens/s at each batch."""
+    import gc
+    from rust_deeplearning_b200 import Engine, random_model
+    from rust_deeplearning_b200.kernels import library
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    engine = Engine(model, max_tokens=max(batches) * (prompt_len + 256), max_seqs=max(batches), max_context=prompt_len + 256)
+    prompt = [int(v) for v in rng.integers(0, vocab, size=prompt_len)]
+    times = []
+    launches = 0
+    for k in range(8):
+        slot = engine.new_sequence()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        before = library.launch_count
+        start.record()
+        engine.step([slot], [prompt], "last")
+        stop.record()
+        torch.cuda.synchronize()
+        launches = library.launch_count - before
+        engine.release(slot)
+        if k >= 3:
+            times.append(start.elapsed_time(stop))
+    out = {"prefill_tokens": prompt_len, "prefill_ms": round(statistics.median(times), 3),
+           "prefill_tok_s": round(prompt_len / (statistics.median(times) * 1e-3), 1), "prefill_launches": launches}
+    for b in batches:
+        ms, n_launch, _ = decode_run(engine, b, steps, warmup, vocab, torch, rng, prompt_len)
+        out[f"decode_b{b}_ms"] = round(ms, 4)
+        out[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+        out[f"decode_b{b}_launches_per_step"] = n_launch // steps
+    engine.check_status()
+    del engine, model
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def design_comparison(args):
+    import numpy as np
+    import torch
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(0)
+    clocks = ClockSampler()
+    clocks.start()
+    sizes = {}
+    for name, (lig, gem) in DESIGN_SIZES.items():
+        if args.size and name != args.size:
+            continue
+        sizes[name] = {
+            "ligirax": design_point(ligirax_shape(**lig), lig["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
+            "gemma2": design_point(gemma_like(**gem), gem["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
+            "shapes": {"ligirax": lig, "gemma2": gem}}
+    print(json.dumps({"design": "ligirax beside gemma2 at equal width, heads and active feed-forward width", "dtype": "bf16",
+                      "data": "synthetic: random weights, seeded uniform-random token ids", "prompt_len": PROMPT,
+                      "sizes": sizes, "clocks": clocks.stop(), "peaks": peaks()}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -241,6 +335,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="batch of the --only decode case")
     ap.add_argument("--context", type=int, default=PROMPT, help="prompt length of the --only decode case")
     ap.add_argument("--no-large", action="store_true", help="leave out the 9B and 27B shapes and the long contexts")
+    ap.add_argument("--design", choices=["ligirax"], default=None,
+                    help="instead of the default workload: prefill and decode of this design beside Gemma 2 at equal layer sizes")
+    ap.add_argument("--size", default=None, help="with --design: one of the sizes only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -253,6 +350,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design is not None:
+        return design_comparison(args)
     if args.steps + args.warmup > NEW_TOKENS - 1:
         args.steps = NEW_TOKENS - 1 - args.warmup
 

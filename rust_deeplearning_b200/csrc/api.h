@@ -211,6 +211,17 @@ int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, 
 int rdl_moe_down_combine(void* out, int dtype, const void* mid, const void* x, const void* w_down, const int* sel,
                          const float* sel_w, int n_rows, int top, int n_real, int ff, int width, void* stream);
 
+// Many rows: every pair with a real expert gets a slot in a buffer sorted by expert, each expert's run padded to whole
+// tiles of 128 rows (max_tiles * 128 >= n_pairs + 127 n_real slots): pair_slot[pair] (-1: identity expert),
+// slot_pair[slot] (-1: padding), tile_group[tile] (-1: not in use).  Then the rows are gathered (bfloat16, width a
+// multiple of 8), multiplied tile by tile (rdl_gemm_tc_grouped) and summed per row with the router's weights.
+int rdl_moe_align(const int* sel, int n_pairs, int n_real, int max_tiles, int* pair_slot, int* slot_pair, int* tile_group, void* stream);
+int rdl_moe_gather(void* xs, const void* x, const int* slot_pair, const int* tile_group, int max_tiles, int top, int width, void* stream);
+int rdl_moe_combine(void* out, const void* y, const void* x, const int* pair_slot, const float* sel_w, int n_rows, int top, int width,
+                    void* stream);
+int rdl_gemm_tc_grouped(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k, int n_groups,
+                        const int* tile_group, int gated, int activation, float act_param, int* status, void* stream);
+
 // sampling over float logits [rows, vocab]
 typedef struct {
     float temperature;          // < 1e-7: greedy

@@ -98,6 +98,12 @@ struct TcArgs {
     int out_dtype, activation;
     float softcap;
     int* status;
+    // grouped form (one block a tile only): row tile i multiplies with group tile_group[i] of a weight matrix that
+    // holds `group_rows` rows per group one after another (gated: a group's N gate rows, then its N up rows);
+    // a negative group marks a row tile that is not in use.  NULL: one group.
+    const int* tile_group;
+    int group_rows;
+    float act_param;           // the parameter of a gated form that has one
 };
 
 
@@ -148,6 +154,10 @@ __device__ __forceinline__ void epilogue_piece(const TcArgs& a, uint32_t taddr, 
         if (a.activation == RDL_ACT_GELU_TANH) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = rdl_activation_fast(v[i], RDL_ACT_GELU_TANH) * u[i];
+        } else if (a.activation == RDL_ACT_SWISH_LIMIT) {
+            const float limit = a.act_param;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = rdl_gated_fast(v[i], u[i], RDL_ACT_SWISH_LIMIT, limit);
         } else {
             const int act = a.activation;
 #pragma unroll
@@ -259,8 +269,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     // barriers and tensor memory were set up while the kernel before was still running; its results are needed from here on
     rdl_grid_wait();
     rdl_grid_launch_dependents();
+    // the grouped form: which rows of the weight matrix this row tile multiplies with (written by a kernel of this step)
+    int w_row0 = n0;
+    bool in_use = true;
+    if (a.tile_group) {
+        const int g = a.tile_group[m0 / BM];
+        in_use = g >= 0;
+        w_row0 = g * a.group_rows + n0;
+    }
 
-    if (warp == 0) {
+    if (!in_use) {
+        // a row tile no group uses: nothing to load, multiply or store
+    } else if (warp == 0) {
         if (lane == 0) {
             // ---- loader ----
             for (int kb = 0; kb < kblocks; ++kb) {
@@ -271,8 +291,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
                 mbar_expect_tx(full, STAGE_BYTES);
                 tma_load_2d(smem_u32(stage), &map_x, kb * BK, m0, full);
-                tma_load_2d(smem_u32(stage + A_BYTES), &map_w, kb * BK, n0, full);
-                if (GATED) tma_load_2d(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + n0, full);
+                tma_load_2d(smem_u32(stage + A_BYTES), &map_w, kb * BK, w_row0, full);
+                if (GATED) tma_load_2d(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + w_row0, full);
             }
         }
     } else if (warp == 1) {
@@ -607,7 +627,7 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
         }
         mw = it->second;
     }
-    TcArgs a{out, m, n, k, out_dtype, activation, softcap, status};
+    TcArgs a{out, m, n, k, out_dtype, activation, softcap, status, nullptr, 0, 0.f};
     cudaStream_t st = (cudaStream_t)stream;
     if (pair) {
         // a second accumulator (the products of a tile run while the tile before it is stored) where a pair
@@ -618,5 +638,39 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
         return pair_tiles > rdl_sm_count() / 2 ? launch_pair<false, 2>(mx, mw, a, st) : launch_pair<false, 1>(mx, mw, a, st);
     }
     if (mt == 2) return gated ? launch_tc<128, true, 2>(mx, mw, a, st) : launch_tc<256, false, 2>(mx, mw, a, st);
+    return gated ? launch_tc<128, true, 1>(mx, mw, a, st) : launch_tc<256, false, 1>(mx, mw, a, st);
+}
+
+// The same product with a weight matrix per group of rows: row tile i (128 rows of x) multiplies with group
+// tile_group[i] (a device array of m / 128 entries, negative: the tile is not in use) of w, which holds n_groups
+// matrices of [n, k] (gated: [2 n, k], gate rows first) one after another.  m is a multiple of 128.  The gated
+// forms are those of rdl_gated (act_param: the parameter of a form that has one).
+extern "C" int rdl_gemm_tc_grouped(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k, int n_groups,
+                                   const int* tile_group, int gated, int activation, float act_param, int* status, void* stream) {
+    RDL_REQUIRE(out && x && w && tile_group, "gemm_tc_grouped: missing operand");
+    RDL_REQUIRE(rdl_valid_dtype(out_dtype), "gemm_tc_grouped: bad output dtype %d", out_dtype);
+    RDL_REQUIRE(m >= 0 && m % BM == 0 && n > 0 && k > 0 && k % 8 == 0 && n_groups > 0,
+                "gemm_tc_grouped: m=%d n=%d k=%d; m must be a multiple of %d and k of 8", m, n, k, BM);
+    RDL_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0,
+                "gemm_tc_grouped: operands must start on 16-byte boundaries");
+    RDL_REQUIRE(!gated || rdl_gated_known(activation), "gemm_tc_grouped: unknown gated form %d", activation);
+    if (m == 0) return 0;
+    const int bn = gated ? 128 : 256;
+    const long long group_rows = gated ? 2LL * n : n;
+    CUtensorMap mx, mw;
+    if (int e = make_map(&mx, x, m, k, BM)) return e;
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        const auto key = std::make_tuple(w, group_rows * n_groups, (long long)k, bn);
+        auto it = g_weight_maps.find(key);
+        if (it == g_weight_maps.end()) {
+            CUtensorMap fresh;
+            if (int e = make_map(&fresh, w, group_rows * n_groups, k, bn)) return e;
+            it = g_weight_maps.emplace(key, fresh).first;
+        }
+        mw = it->second;
+    }
+    TcArgs a{out, m, n, k, out_dtype, activation, 0.f, status, tile_group, (int)group_rows, act_param};
+    cudaStream_t st = (cudaStream_t)stream;
     return gated ? launch_tc<128, true, 1>(mx, mw, a, st) : launch_tc<256, false, 1>(mx, mw, a, st);
 }

@@ -81,6 +81,69 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __res
 
 constexpr int PAIR_WARPS = 8;
 
+// A lane's share of sum_i a[i] * b[i] (and of a second row a2 with the same b): 16-byte loads where n and the
+// addresses allow (bfloat16: 8 values, float: 4), else value by value.  Which form runs depends on n and on where
+// rows start, never on the step's row count.
+template <typename T> struct Piece;
+template <> struct Piece<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+    }
+};
+template <> struct Piece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+};
+template <typename T>
+__device__ __forceinline__ bool pieces_ok(const T* a, const T* b, int n) {
+    return n % Piece<T>::N == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
+}
+template <typename T>
+__device__ __forceinline__ void lane_dot2(const T* a1, const T* a2, const T* b, int n, int lane, float& s1, float& s2) {
+    constexpr int N = Piece<T>::N;
+    s1 = 0.f; s2 = 0.f;
+    if (pieces_ok(a1, b, n) && (((uintptr_t)a2) & 15) == 0) {
+        for (int i = lane * N; i < n; i += 32 * N) {
+            float x[N], w1[N], w2[N];
+            Piece<T>::load(b + i, x);
+            Piece<T>::load(a1 + i, w1);
+            Piece<T>::load(a2 + i, w2);
+#pragma unroll
+            for (int j = 0; j < N; ++j) { s1 = fmaf(w1[j], x[j], s1); s2 = fmaf(w2[j], x[j], s2); }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            const float x = to_float(b[i]);
+            s1 = fmaf(to_float(a1[i]), x, s1);
+            s2 = fmaf(to_float(a2[i]), x, s2);
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ float lane_dot(const T* a, const T* b, int n, int lane) {
+    constexpr int N = Piece<T>::N;
+    float s = 0.f;
+    if (pieces_ok(a, b, n)) {
+        for (int i = lane * N; i < n; i += 32 * N) {
+            float x[N], w[N];
+            Piece<T>::load(b + i, x);
+            Piece<T>::load(a + i, w);
+#pragma unroll
+            for (int j = 0; j < N; ++j) s = fmaf(w[j], x[j], s);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(to_float(a[i]), to_float(b[i]), s);
+    }
+    return s;
+}
+
 // mid[p, j] = act(W_gate[e] x, W_up[e] x)[j] for pair p = (row t, choice k) with expert e = sel[p] < n_real.
 // w: [n_real][2 ff][width], an expert's gate rows followed by its up rows.  A warp per (pair, j).
 template <typename T>
@@ -97,12 +160,8 @@ __global__ void __launch_bounds__(PAIR_WARPS * 32) moe_gate_up_kernel(T* __restr
     const T* row = x + (long long)(p / top) * width;
     const T* wg = w + ((long long)e * 2 * ff + j) * width;
     const T* wu = wg + (long long)ff * width;
-    float g = 0.f, u = 0.f;
-    for (int k = lane; k < width; k += 32) {
-        const float xv = to_float(row[k]);
-        g = fmaf(to_float(wg[k]), xv, g);
-        u = fmaf(to_float(wu[k]), xv, u);
-    }
+    float g, u;
+    lane_dot2<T>(wg, wu, row, width, lane, g, u);
     g = warp_sum(g);
     u = warp_sum(u);
     if (lane == 0) mid[(long long)p * ff + j] = from_float<T>(rdl_gated(g, u, activation, act_param));
@@ -130,13 +189,117 @@ __global__ void __launch_bounds__(PAIR_WARPS * 32) moe_down_combine_kernel(T* __
         } else {
             const T* w = w_down + ((long long)e * width + n) * ff;
             const T* m = mid + (long long)p * ff;
-            float acc = 0.f;
-            for (int i = lane; i < ff; i += 32) acc = fmaf(to_float(w[i]), to_float(m[i]), acc);
-            y = warp_sum(acc);
+            y = warp_sum(lane_dot<T>(w, m, ff, lane));
         }
         total = fmaf(wk, y, total);
     }
     if (lane == 0) out[(long long)t * width + n] = from_float<T>(total);
+}
+
+// ---- many rows: sorted by expert, one expert per tile of MOE_TILE rows ----
+
+constexpr int MOE_TILE = 128, ALIGN_THREADS = 1024;
+
+// Gives every (row, choice) pair with a real expert a slot in a buffer in which each expert's pairs lie together,
+// every expert's run padded to whole tiles: pair_slot[p] (-1: an identity expert), slot_pair[s] (-1: padding),
+// tile_group[tile] (the tile's expert; -1: not in use).  One block; shared memory: 3 n_real + 1 ints.
+__global__ void __launch_bounds__(ALIGN_THREADS) moe_align_kernel(const int* __restrict__ sel, int n_pairs, int n_real, int max_tiles,
+                                                                  int* __restrict__ pair_slot, int* __restrict__ slot_pair,
+                                                                  int* __restrict__ tile_group) {
+    extern __shared__ int ws[];
+    int* counts = ws;
+    int* offsets = ws + n_real;            // n_real + 1 entries
+    int* cursor = ws + 2 * n_real + 1;
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    for (int e = threadIdx.x; e < n_real; e += ALIGN_THREADS) { counts[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += ALIGN_THREADS) {
+        const int e = sel[p];
+        if (e >= 0 && e < n_real) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0;
+        for (int e = 0; e < n_real; ++e) {
+            offsets[e] = off;
+            off += (counts[e] + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+        }
+        offsets[n_real] = off;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < max_tiles; t += ALIGN_THREADS) {
+        const int row = t * MOE_TILE;
+        int g = -1;
+        if (row < offsets[n_real]) {
+            int lo = 0, hi = n_real - 1;   // the last expert whose run starts at or before the row (empty runs start where the next one does)
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (offsets[mid] <= row) lo = mid; else hi = mid - 1;
+            }
+            g = lo;
+        }
+        tile_group[t] = g;
+    }
+    for (int s = threadIdx.x; s < max_tiles * MOE_TILE; s += ALIGN_THREADS) slot_pair[s] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += ALIGN_THREADS) {
+        const int e = sel[p];
+        int slot = -1;
+        if (e >= 0 && e < n_real) {
+            slot = offsets[e] + atomicAdd(&cursor[e], 1);
+            slot_pair[slot] = p;
+        }
+        pair_slot[p] = slot;
+    }
+}
+
+// xs[slot, :] = x[pair / top, :] (zeros in padding slots of tiles in use); 16-byte pieces
+__global__ void moe_gather_kernel(uint4* __restrict__ xs, const uint4* __restrict__ x, const int* __restrict__ slot_pair,
+                                  const int* __restrict__ tile_group, int top, int pieces) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int slot = blockIdx.x;
+    if (tile_group[slot / MOE_TILE] < 0) return;
+    const int p = slot_pair[slot];
+    uint4* dst = xs + (long long)slot * pieces;
+    if (p < 0) {
+        for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    } else {
+        const uint4* src = x + (long long)(p / top) * pieces;
+        for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// out[t, :] = sum_k sel_w[t, k] * (pair_slot[(t, k)] >= 0 ? y[slot, :] : x[t, :]), k in rising order, float sums
+__global__ void moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x,
+                                   const int* __restrict__ pair_slot, const float* __restrict__ sel_w, int top, int width) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int slot = pair_slot[t * top + k];
+            const float wk = sel_w[t * top + k];
+            const __nv_bfloat16* src = slot >= 0 ? y + (long long)slot * width + c : x + (long long)t * width + c;
+            const uint4 raw = *reinterpret_cast<const uint4*>(src);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 v = __bfloat1622float2(h[i]);
+                acc[2 * i] = fmaf(wk, v.x, acc[2 * i]);
+                acc[2 * i + 1] = fmaf(wk, v.y, acc[2 * i + 1]);
+            }
+        }
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        *reinterpret_cast<uint4*>(out + (long long)t * width + c) = raw;
+    }
 }
 
 }  // namespace
@@ -192,5 +355,37 @@ extern "C" int rdl_moe_down_combine(void* out, int dtype, const void* mid, const
     else
         RDL_CHECK_EX(rdl_launch(moe_down_combine_kernel<float>, grid, dim3(PAIR_WARPS * 32), 0, st, (float*)out, (const float*)mid, (const float*)x,
                                 (const float*)w_down, sel, sel_w, top, n_real, ff, width), "moe_down_combine");
+    return 0;
+}
+
+extern "C" int rdl_moe_align(const int* sel, int n_pairs, int n_real, int max_tiles, int* pair_slot, int* slot_pair, int* tile_group,
+                             void* stream) {
+    RDL_REQUIRE(sel && pair_slot && slot_pair && tile_group && n_pairs > 0 && n_real > 0 && max_tiles > 0, "moe_align: bad arguments");
+    RDL_REQUIRE((long long)max_tiles * MOE_TILE >= (long long)n_pairs + (long long)n_real * (MOE_TILE - 1),
+                "moe_align: %d tiles cannot hold %d pairs of %d experts", max_tiles, n_pairs, n_real);
+    RDL_REQUIRE(n_real <= 4096, "moe_align: %d experts exceed the 4,096 the kernel holds", n_real);
+    const size_t smem = (3 * (size_t)n_real + 1) * sizeof(int);
+    RDL_CHECK_EX(rdl_launch(moe_align_kernel, dim3(1), dim3(ALIGN_THREADS), smem, (cudaStream_t)stream, sel, n_pairs, n_real, max_tiles, pair_slot,
+                            slot_pair, tile_group), "moe_align");
+    return 0;
+}
+
+extern "C" int rdl_moe_gather(void* xs, const void* x, const int* slot_pair, const int* tile_group, int max_tiles, int top, int width,
+                              void* stream) {
+    RDL_REQUIRE(xs && x && slot_pair && tile_group && max_tiles > 0 && top > 0 && width > 0 && width % 8 == 0,
+                "moe_gather: bad arguments (bfloat16 rows of a multiple of 8 values)");
+    RDL_REQUIRE((uintptr_t)xs % 16 == 0 && (uintptr_t)x % 16 == 0, "moe_gather: rows must start on 16-byte boundaries");
+    RDL_CHECK_EX(rdl_launch(moe_gather_kernel, dim3(max_tiles * MOE_TILE), dim3(128), 0, (cudaStream_t)stream, (uint4*)xs, (const uint4*)x, slot_pair,
+                            tile_group, top, width / 8), "moe_gather");
+    return 0;
+}
+
+extern "C" int rdl_moe_combine(void* out, const void* y, const void* x, const int* pair_slot, const float* sel_w, int n_rows, int top,
+                               int width, void* stream) {
+    RDL_REQUIRE(out && y && x && pair_slot && sel_w && n_rows > 0 && top > 0 && width > 0 && width % 8 == 0,
+                "moe_combine: bad arguments (bfloat16 rows of a multiple of 8 values)");
+    RDL_REQUIRE((uintptr_t)out % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)x % 16 == 0, "moe_combine: rows must start on 16-byte boundaries");
+    RDL_CHECK_EX(rdl_launch(moe_combine_kernel, dim3(n_rows), dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)y,
+                            (const __nv_bfloat16*)x, pair_slot, sel_w, top, width), "moe_combine");
     return 0;
 }

@@ -271,6 +271,10 @@ _SIGNATURES = {
     "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "rdl_moe_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "rdl_moe_down_combine": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "rdl_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P],
+    "rdl_moe_gather": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "rdl_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "rdl_gemm_tc_grouped": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P],
 }
 
 _lib = None

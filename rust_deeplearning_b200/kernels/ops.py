@@ -863,6 +863,46 @@ def moe_experts_few(x: torch.Tensor, sel: torch.Tensor, sel_w: torch.Tensor, w_g
     return out
 
 
+MOE_TILE = 128               # rows of a tile of the grouped product: one expert per tile
+MOE_GROUPED_MIN_PAIRS = 128  # from this many (row, choice) pairs on the rows are sorted by expert
+
+
+def moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param: float,
+                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The routed experts for many rows in bfloat16: pairs sorted by expert into tiles of 128 rows, both products on the
+    tcgen05 kernel with one expert per row tile, then the weighted sum per row.  No step of it needs the host to
+    know the counts: the buffers are sized for the worst case and tiles no expert uses are skipped."""
+    T, width = x.shape
+    top = sel.shape[1]
+    ff = w_gate_up.shape[1] // 2
+    pairs = T * top
+    max_tiles = (pairs + n_real * (MOE_TILE - 1) + MOE_TILE - 1) // MOE_TILE
+    dev = x.device
+    pair_slot = torch.empty(pairs, dtype=torch.int32, device=dev)
+    slot_pair = torch.empty(max_tiles * MOE_TILE, dtype=torch.int32, device=dev)
+    tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    lib = library.load()
+    st = _stream(x)
+    library.check(lib.rdl_moe_align(_ptr(sel), pairs, n_real, max_tiles, _ptr(pair_slot), _ptr(slot_pair), _ptr(tile_group), st))
+    xs = torch.empty((max_tiles * MOE_TILE, width), dtype=x.dtype, device=dev)
+    library.check(lib.rdl_moe_gather(_ptr(xs), _ptr(x), _ptr(slot_pair), _ptr(tile_group), max_tiles, top, width, st))
+    mid = torch.empty((max_tiles * MOE_TILE, ff), dtype=x.dtype, device=dev)
+    library.check(lib.rdl_gemm_tc_grouped(_ptr(mid), _dtype_code(mid), _ptr(xs), _ptr(w_gate_up), max_tiles * MOE_TILE, ff, width, n_real,
+                                          _ptr(tile_group), 1, GATED_FORMS[form], float(param), _status(status), st))
+    y = torch.empty((max_tiles * MOE_TILE, width), dtype=x.dtype, device=dev)
+    library.check(lib.rdl_gemm_tc_grouped(_ptr(y), _dtype_code(y), _ptr(mid), _ptr(w_down), max_tiles * MOE_TILE, width, ff, n_real,
+                                          _ptr(tile_group), 0, 0, 0.0, _status(status), st))
+    out = torch.empty_like(x)
+    library.check(lib.rdl_moe_combine(_ptr(out), _ptr(y), _ptr(x), _ptr(pair_slot), _ptr(sel_w), T, top, width, st))
+    return out
+
+
 def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param: float) -> torch.Tensor:
-    """The routed experts' weighted sum for every row (see `moe_experts_few` for the meaning of the arguments)."""
+    """The routed experts' weighted sum for every row (see `moe_experts_few` for the meaning of the arguments): with
+    few pairs each streams its expert's matrices; with many, in bfloat16, the rows are sorted by expert and multiplied
+    tile by tile (`moe_experts_grouped`)."""
+    T, width = x.shape
+    if (n_real and x.dtype is torch.bfloat16 and T * sel.shape[1] >= MOE_GROUPED_MIN_PAIRS and width % 8 == 0
+            and w_gate_up.shape[1] % 16 == 0 and x.is_contiguous() and x.data_ptr() % 16 == 0):
+        return moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)
     return moe_experts_few(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)
