@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 12
+#define RDL_ABI_VERSION 13
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -200,10 +200,21 @@ typedef struct {
 } HeadsLinearArgs;
 int rdl_heads_linear(const HeadsLinearArgs* a, void* stream);
 
+// Decode attention of the absorbed form on tensor cores (csrc/latent_decode.cu): q [tokens][heads * width] attends over
+// the cached rows [pages][1][page_size][width] (bfloat16) as keys and, in their first kv_rank values, as values; the
+// first kv_rank values of every head of out [tokens][heads * width] are written.  n_splits blocks share a token's
+// keys (scratch of rdl_latent_decode_scratch_bytes when > 1).
+long long rdl_latent_decode_scratch_bytes(int n_tokens, int n_heads, int kv_rank, int n_splits);
+int rdl_latent_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* cache, const int* tables,
+                      int table_width, int page_size, int ring_pages, const int* tok_seq, const int* tok_pos, int n_tokens,
+                      int n_heads, int width, int kv_rank, float score_scale, int window, int max_keys, int n_splits,
+                      void* scratch, long long scratch_bytes, void* stream);
+
 // ---- routed feed-forward (csrc/moe.cu) ----
-// sel[t, k], sel_w[t, k]: the `top` experts of row t by softmax score + correction, and their softmax scores
+// sel[t, k], sel_w[t, k]: the `top` experts of row t by softmax score + correction, and their softmax scores;
+// logits: float work space [rows][experts] (two kernels: the logits, then softmax and choice)
 int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
-                  int width, int top, int* sel, float* sel_w, void* stream);
+                  int width, int top, int* sel, float* sel_w, float* logits, void* stream);
 // mid[(t, k), :] = gated(W_gate[e] x_t, W_up[e] x_t) for e = sel[t, k] < n_real; w_gate_up [n_real][2 ff][width]
 int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, const int* sel, int n_rows, int top, int n_real,
                     int ff, int width, int activation, float act_param, void* stream);

@@ -18,33 +18,74 @@
 
 namespace {
 
-constexpr int ROUTE_THREADS = 128;
+// Router logits z[t, e] = W_r[e, :] . x[t, :] in float.  A block takes ROUTE_ROWS rows and 8 experts, a warp one
+// expert for all of the block's rows: a weight row is read once for them, lanes split k (16-byte pieces where the width
+// allows), and the sum of a (row, expert) ends in a shuffle tree: its order depends on the width alone.
+constexpr int ROUTE_ROWS = 8, ROUTE_WARPS = 8;
 
 template <typename T>
-__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
-                                                                  const float* __restrict__ correction, int n_experts, int width, int top,
-                                                                  int* __restrict__ sel, float* __restrict__ sel_w) {
-    extern __shared__ float zs[];              // [n_experts] logits, then scores; [n_experts] choice
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(const T* __restrict__ x, const float* __restrict__ w_router, int n_rows,
+                                                                      int n_experts, int width, float* __restrict__ z) {
     rdl_grid_wait();
     rdl_grid_launch_dependents();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* row = x + (long long)t * width;
-    for (int e = warp; e < n_experts; e += ROUTE_THREADS / 32) {
-        const float* w = w_router + (long long)e * width;
-        float acc = 0.f;
-        for (int k = lane; k < width; k += 32) acc = fmaf(w[k], to_float(row[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) zs[e] = acc;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * ROUTE_ROWS, e = blockIdx.y * ROUTE_WARPS + warp;
+    if (e >= n_experts) return;
+    const int rows = min(ROUTE_ROWS, n_rows - t0);
+    const float* w = w_router + (long long)e * width;
+    float acc[ROUTE_ROWS];
+#pragma unroll
+    for (int r = 0; r < ROUTE_ROWS; ++r) acc[r] = 0.f;
+    if (width % 4 == 0 && ((uintptr_t)w & 15) == 0) {
+        for (int k = lane * 4; k < width; k += 128) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + k);
+#pragma unroll
+            for (int r = 0; r < ROUTE_ROWS; ++r) {
+                if (r < rows) {
+                    const T* row = x + (long long)(t0 + r) * width + k;
+                    acc[r] = fmaf(wv.x, to_float(row[0]), acc[r]);
+                    acc[r] = fmaf(wv.y, to_float(row[1]), acc[r]);
+                    acc[r] = fmaf(wv.z, to_float(row[2]), acc[r]);
+                    acc[r] = fmaf(wv.w, to_float(row[3]), acc[r]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < width; k += 32) {
+            const float wv = w[k];
+#pragma unroll
+            for (int r = 0; r < ROUTE_ROWS; ++r)
+                if (r < rows) acc[r] = fmaf(wv, to_float(x[(long long)(t0 + r) * width + k]), acc[r]);
+        }
     }
-    __syncthreads();
-    if (warp != 0) return;
+#pragma unroll
+    for (int r = 0; r < ROUTE_ROWS; ++r) {
+        if (r >= rows) break;
+        const float v = warp_sum(acc[r]);
+        if (lane == 0) z[(long long)(t0 + r) * n_experts + e] = v;
+    }
+}
+
+// softmax over a row's logits, choice = score + correction, the `top` largest choices: a warp per row
+constexpr int TOPK_WARPS = 4;
+
+__global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n_rows,
+                                                                   int n_experts, int top, int* __restrict__ sel, float* __restrict__ sel_w) {
+    extern __shared__ float zs_all[];          // per warp: [n_experts] scores, [n_experts] choices
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * TOPK_WARPS + warp;
+    if (t >= n_rows) return;
+    float* zs = zs_all + (size_t)warp * 2 * n_experts;
     float* choice = zs + n_experts;
+    const float* zr = z + (long long)t * n_experts;
     float m = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, zs[e]);
+    for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, zr[e]);
     m = warp_max(m);
     float sum = 0.f;
     for (int e = lane; e < n_experts; e += 32) {
-        const float p = expf(zs[e] - m);
+        const float p = expf(zr[e] - m);
         zs[e] = p;
         sum += p;
     }
@@ -305,20 +346,23 @@ __global__ void moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_b
 }  // namespace
 
 extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
-                             int width, int top, int* sel, float* sel_w, void* stream) {
+                             int width, int top, int* sel, float* sel_w, float* logits, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "moe_route: bad dtype %d", dtype);
-    RDL_REQUIRE(x && w_router && sel && sel_w && n_experts > 0 && width > 0, "moe_route: bad arguments");
+    RDL_REQUIRE(x && w_router && sel && sel_w && logits && n_experts > 0 && width > 0, "moe_route: bad arguments");
     RDL_REQUIRE(top >= 1 && top <= n_experts, "moe_route: %d of %d experts cannot be chosen", top, n_experts);
-    RDL_REQUIRE(n_experts <= 4096, "moe_route: %d experts exceed the 4,096 the router kernel holds", n_experts);
+    RDL_REQUIRE(n_experts <= 1024, "moe_route: %d experts exceed the 1,024 the router kernels hold", n_experts);
     if (n_rows == 0) return 0;
-    const size_t smem = 2 * (size_t)n_experts * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid((n_rows + ROUTE_ROWS - 1) / ROUTE_ROWS, (n_experts + ROUTE_WARPS - 1) / ROUTE_WARPS);
     if (dtype == RDL_BF16)
-        RDL_CHECK_EX(rdl_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_rows), dim3(ROUTE_THREADS), smem, st, (const __nv_bfloat16*)x, w_router,
-                                correction, n_experts, width, top, sel, sel_w), "moe_route");
+        RDL_CHECK_EX(rdl_launch(moe_logits_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), 0, st, (const __nv_bfloat16*)x, w_router, n_rows,
+                                n_experts, width, logits), "moe_route");
     else
-        RDL_CHECK_EX(rdl_launch(moe_route_kernel<float>, dim3(n_rows), dim3(ROUTE_THREADS), smem, st, (const float*)x, w_router, correction,
-                                n_experts, width, top, sel, sel_w), "moe_route");
+        RDL_CHECK_EX(rdl_launch(moe_logits_kernel<float>, grid, dim3(ROUTE_WARPS * 32), 0, st, (const float*)x, w_router, n_rows, n_experts, width,
+                                logits), "moe_route");
+    const size_t smem = (size_t)TOPK_WARPS * 2 * n_experts * sizeof(float);
+    RDL_CHECK_EX(rdl_launch(moe_topk_kernel, dim3((n_rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(TOPK_WARPS * 32), smem, st, (const float*)logits,
+                            correction, n_rows, n_experts, top, sel, sel_w), "moe_route");
     return 0;
 }
 

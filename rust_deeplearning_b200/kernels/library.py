@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 12
+ABI_VERSION = 13
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -268,7 +268,8 @@ _SIGNATURES = {
     "rdl_latent_assemble": [_P, _I, _P, _LL, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "rdl_gate_heads": [_P, _I, _P, _LL, _I, _P, _LL, _I, _I, _I, _P],
     "rdl_heads_linear": [ctypes.POINTER(HeadsLinearArgs), _P],
-    "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+    "rdl_latent_decode": [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _LL, _P],
+    "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P],
     "rdl_moe_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "rdl_moe_down_combine": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "rdl_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P],
@@ -306,6 +307,8 @@ def load():
         lib.rdl_attention_decode_counter_bytes.argtypes = [_I, _I]
         lib.rdl_attention_decode_counter_bytes.restype = _LL
         lib.rdl_attention_decode_scratch_bytes.restype = _LL
+        lib.rdl_latent_decode_scratch_bytes.argtypes = [_I, _I, _I, _I]
+        lib.rdl_latent_decode_scratch_bytes.restype = _LL
         lib.rdl_sampling_uniform.argtypes = [ctypes.c_ulonglong] * 3
         lib.rdl_sampling_uniform.restype = ctypes.c_float
         lib.rdl_set_programmatic_launch.argtypes = [ctypes.c_int]

@@ -806,6 +806,42 @@ def heads_linear(x: torch.Tensor, x_col: int, x_head: int, w: torch.Tensor, out:
     return out
 
 
+def latent_decode_ok(dtype, width: int, kv_rank: int, page_size: int) -> bool:
+    """Whether the tensor-core decode kernel of the absorbed form takes these sizes."""
+    return (dtype is torch.bfloat16 and width % 16 == 0 and width <= 640 and kv_rank % 16 == 0 and 0 < kv_rank <= min(512, width)
+            and page_size % 8 == 0)
+
+
+def latent_decode(q: torch.Tensor, b: AttentionBatch, pages: KVPages, *, n_heads: int, kv_rank: int, score_scale: float,
+                  window: Optional[int], scratch=None, n_splits: Optional[int] = None) -> torch.Tensor:
+    """Single-token attention of the absorbed form: q [tokens, n_heads * width] (width = kv_rank + rot_dim) over the
+    cached rows `pages.k` [pages, 1, page_size, width], which are keys and, in their first kv_rank values, values.
+    Returns [tokens, n_heads * width] whose first kv_rank values per head hold the result (the rest is not written).
+    scratch: callable(nbytes) -> float32 tensor for the partial results when a token's keys are shared between blocks."""
+    _dense(q, "q")
+    T = q.shape[0]
+    width = pages.k.shape[3]
+    _need(q.dtype is torch.bfloat16 and pages.k.dtype is torch.bfloat16 and q.shape[1] == n_heads * width
+          and tuple(pages.k.shape[1:3]) == (1, pages.page_size) and pages.k.is_contiguous(), "latent_decode: shapes do not fit")
+    out = torch.empty_like(q)
+    groups = (n_heads + 15) // 16
+    tiles = (max(b.max_keys, 1) + 63) // 64 + 1
+    # about two blocks per multiprocessor, a block per 64 keys at most
+    splits = max(1, min(tiles, (2 * sm_count(q.device.index or 0)) // max(1, b.n_tokens * groups)))
+    if n_splits is not None:
+        splits = max(1, min(tiles, n_splits))
+    lib = library.load()
+    need = lib.rdl_latent_decode_scratch_bytes(b.n_tokens, n_heads, kv_rank, splits)
+    buf = None
+    if need:
+        buf = scratch(need) if scratch is not None else torch.empty(-(-need // 4), dtype=torch.float32, device=q.device)
+    library.check(lib.rdl_latent_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(pages.k), _ptr(pages.tables), pages.tables.shape[1],
+                                        pages.page_size, pages.ring_pages, _ptr(b.tok_seq), _ptr(b.tok_pos), b.n_tokens, n_heads, width,
+                                        kv_rank, float(score_scale), int(window or 0), max(b.max_keys, 1), splits, _ptr(buf),
+                                        buf.numel() * 4 if buf is not None else 0, _stream(q)), 2 if splits > 1 else 1)
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 # routed feed-forward
 # ------------------------------------------------------------------------------------------
@@ -824,8 +860,9 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
         _need(correction.dtype is torch.float32 and correction.is_contiguous() and correction.numel() == E, "moe_route: float32 correction [experts]")
     sel = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
     sel_w = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
+    logits = torch.empty((x.shape[0], E), dtype=torch.float32, device=x.device)
     library.check(library.load().rdl_moe_route(_ptr(x), _dtype_code(x), _ptr(w_router), _ptr(correction), x.shape[0], E, x.shape[1], top,
-                                               _ptr(sel), _ptr(sel_w), _stream(x)))
+                                               _ptr(sel), _ptr(sel_w), _ptr(logits), _stream(x)), 2)
     return sel, sel_w
 
 

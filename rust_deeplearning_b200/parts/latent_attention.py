@@ -24,6 +24,7 @@ Every size, the score scale, the window and the position encoding are parameters
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -33,6 +34,11 @@ from ..kernels import ops
 from .attention import cache_owner
 from .registry import BuildContext, build_part, register_part
 from .spec import PartSpec
+
+
+# "own": single-token steps use the decode kernel written for one cached row per token; "generic": the ordinary decode
+# kernel with one key/value head where its sizes allow (for comparison; set RDL_LATENT_DECODE=generic)
+LATENT_DECODE = os.environ.get("RDL_LATENT_DECODE", "own")
 
 
 def _round_up(n: int, m: int) -> int:
@@ -118,11 +124,16 @@ class LatentAttention:
         ops.heads_linear(rows, 0, d + rd, self.w_uk_t, out=qp, out_col=0, out_head=width)
         common = dict(n_heads=H, n_kv_heads=1, head_dim=width, score_scale=self.score_scale, softcap=None, window=self.window)
         if batch.is_decode or (not cache.owns_kv and owner_rows is None):
-            fast = bf16 and batch.is_decode and H <= 8 and width % 16 == 0 and width <= 256 \
-                and cache.page_size % 16 == 0 and cache.page_size <= 64
             ab = batch.attention_batch("all", self.window)
-            ctx = ops.attention(qp, ab, pages, kind="decode" if fast else "plain",
-                                scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
+            generic = bf16 and batch.is_decode and H <= 8 and width % 16 == 0 and width <= 256 \
+                and cache.page_size % 16 == 0 and cache.page_size <= 64
+            if batch.is_decode and LATENT_DECODE == "own" and ops.latent_decode_ok(rows.dtype, width, r, cache.page_size):
+                # all heads of a token share the cached rows a block has brought in
+                ctx = ops.latent_decode(qp, ab, pages, n_heads=H, kv_rank=r, score_scale=self.score_scale, window=self.window,
+                                        scratch=lambda n: batch.scratch_buffer("latent_decode", n))
+            else:
+                ctx = ops.attention(qp, ab, pages, kind="decode" if generic else "plain",
+                                    scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
         else:
             if cache.owns_kv:
                 if run in batch.shared_runs:

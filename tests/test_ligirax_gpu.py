@@ -146,6 +146,57 @@ def test_router_and_experts(dtype, rows, shape):
     _close(got[torch.tensor(safe, device=DEV)], want[safe], dtype, "routed experts")
 
 
+@pytest.mark.parametrize("case", [
+    # heads, kv_rank, rot_dim, page, window, splits
+    (6, 32, 16, 16, 9, 1), (6, 32, 16, 16, 9, 3), (16, 96, 32, 64, 72, None), (20, 48, 16, 8, None, 2), (3, 448, 64, 64, 200, None),
+    (17, 256, 64, 32, None, 5), (1, 16, 16, 16, 64, 1)])
+def test_latent_decode_kernel_against_the_plain_kernel(case):
+    """The tensor-core decode kernel of the absorbed form against the float kernel: pages in random order, sequences of
+    unequal lengths, a padding row, one split and several.  In every sequence one key is made to dominate: the first key
+    the window keeps, the key just outside it, the newest key, a key at a page's edge, in turn."""
+    from rust_deeplearning_b200.kernels import ops
+    H, r, rd, page, window, splits = case
+    width = r + rd
+    rng = np.random.default_rng(sum(case[:4]))
+    lens = [1, 5, page, page + 1, 150, 333, 64, 65]
+    T = len(lens) + 1
+    n_pages = sum(-(-n // page) for n in lens) + 2
+    cache = torch.tensor(rng.normal(size=(n_pages, 1, page, width)) * 0.5, dtype=torch.float32).to(DEV).to(torch.bfloat16)
+    order = rng.permutation(n_pages)
+    tw = max(-(-n // page) for n in lens)
+    tables = np.zeros((T, tw), dtype=np.int32)
+    at = 0
+    for i, n in enumerate(lens):
+        k = -(-n // page)
+        tables[i, :k] = order[at:at + k]
+        at += k
+    q = torch.tensor(rng.normal(size=(T, H * width)) * 0.5, dtype=torch.float32).to(DEV).to(torch.bfloat16)
+    # the dominating key: a cached row that equals a multiple of head 0's query
+    for i, n in enumerate(lens):
+        p = n - 1
+        lo = max(0, p - window + 1) if window else 0
+        target = [lo, lo - 1, p, (p // page) * page, max(lo, (p // page) * page - 1)][i % 5]
+        if 0 <= target <= p:
+            row = q[i, :width].float() * 6.0
+            pg, rr = tables[i, target // page], target % page
+            sw = torch.empty(width, dtype=torch.float32, device=DEV)
+            for c in range(width // 8):      # the stored row has its 16-byte chunks swizzled by its place in the page
+                cc = (c ^ (rr & 7)) if (c | 7) < width // 8 else c
+                sw[cc * 8:cc * 8 + 8] = row[c * 8:c * 8 + 8]
+            cache[pg, 0, rr] = sw.to(torch.bfloat16)
+    ti = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    pos = [n - 1 for n in lens] + [-1]
+    ab = ops.AttentionBatch(T, T, ti(list(range(T))), ti(pos), ti(list(range(T + 1))), ti(pos[:-1] + [0]), ti(lens + [0]),
+                            max_keys=min(max(lens), window or max(lens)))
+    pages = ops.KVPages(cache, cache, ti(tables), page, tw)
+    want = ops.attention(q, ab, pages, n_heads=H, n_kv_heads=1, head_dim=width, score_scale=0.3, softcap=None, window=window, kind="plain")
+    got = ops.latent_decode(q, ab, pages, n_heads=H, kv_rank=r, score_scale=0.3, window=window, n_splits=splits)
+    w = want.float().view(T, H, width)[:-1, :, :r]
+    g = got.float().view(T, H, width)[:-1, :, :r]
+    assert torch.isfinite(g).all()
+    assert (g - w).abs().max().item() <= 0.02 * max(1.0, w.abs().max().item()), (g - w).abs().max().item()
+
+
 # ---- the model ----
 
 @pytest.mark.parametrize("dtype", DTYPES)
