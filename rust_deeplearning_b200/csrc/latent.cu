@@ -57,11 +57,23 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(LatentPrepar
     const float* cs = a.cos_t + (long long)pos * half;
     const float* sn = a.sin_t + (long long)pos * half;
     const int hq = a.dim + a.rot_dim;
-    // queries: the rotated part of each head, in place or into the rows of the absorbed form
-    for (int h = 0; h < a.n_heads; ++h) {
-        const T* src = row + a.q_col + (long long)h * hq + a.dim;
-        T* dst = a.q_rot_out ? (T*)a.q_rot_out + (long long)t * a.q_rot_stride + (long long)h * a.q_rot_head : (T*)src;
-        rotate_into<T>(src, dst, a.rot_n, a.rot_dim, a.interleaved, cs, sn, threadIdx.x, LP_THREADS);
+    // queries: the rotated part of each head, in place or into the rows of the absorbed form; a work item is one
+    // rotated pair, or one value of the part's unrotated tail that is only copied
+    {
+        const int tail = a.q_rot_out ? a.rot_dim - a.rot_n : 0, per_head = half + tail;
+        for (int idx = threadIdx.x; idx < a.n_heads * per_head; idx += LP_THREADS) {
+            const int h = idx / per_head, i = idx - h * per_head;
+            const T* src = row + a.q_col + (long long)h * hq + a.dim;
+            T* dst = a.q_rot_out ? (T*)a.q_rot_out + (long long)t * a.q_rot_stride + (long long)h * a.q_rot_head : (T*)src;
+            if (i < half) {
+                const int pa = a.interleaved ? 2 * i : i, pb = a.interleaved ? 2 * i + 1 : i + half;
+                const float u = to_float(src[pa]), v = to_float(src[pb]);
+                dst[pa] = from_float<T>(u * cs[i] - v * sn[i]);
+                dst[pb] = from_float<T>(v * cs[i] + u * sn[i]);
+            } else {
+                dst[a.rot_n + i - half] = src[a.rot_n + i - half];
+            }
+        }
     }
     if (a.latent_col < 0) return;              // a layer that reads another layer's latent rows
     // the latent: root mean square in float, a fixed order of additions
@@ -135,6 +147,52 @@ __global__ void latent_assemble_kernel(T* __restrict__ out, const T* __restrict_
     }
 }
 
+// The same in 16-byte pieces of PIECE values, where every size is a whole number of pieces and every row starts on a
+// 16-byte boundary: a grid-stride loop over the pieces of all tokens.
+template <typename T>
+__global__ void latent_assemble_vec_kernel(uint4* __restrict__ out, const T* __restrict__ rows, long long row_stride, int q_col,
+                                           const T* __restrict__ kv, const T* __restrict__ latent, int n_tokens, int n_heads, int dim,
+                                           int rot_dim, int vdim, int kv_rank, int pad) {
+    constexpr int PIECE = 16 / (int)sizeof(T);
+    const int hq = dim + rot_dim, pp = pad / PIECE, per = n_heads * pp;
+    const long long total = 3LL * per * n_tokens;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / (3 * per)), i = (int)(idx - (long long)t * 3 * per);
+        const int part = i / per, j = i - part * per, h = j / pp, e = (j - h * pp) * PIECE;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (part == 0) {
+            if (e < hq) v = *reinterpret_cast<const uint4*>(rows + (long long)t * row_stride + q_col + (long long)h * hq + e);
+        } else if (part == 1) {
+            if (e < dim) v = *reinterpret_cast<const uint4*>(kv + (long long)t * n_heads * (dim + vdim) + (long long)h * dim + e);
+            else if (e < hq) v = *reinterpret_cast<const uint4*>(latent + (long long)t * (kv_rank + rot_dim) + kv_rank + e - dim);
+        } else {
+            if (e < vdim) v = *reinterpret_cast<const uint4*>(kv + (long long)t * n_heads * (dim + vdim) + (long long)n_heads * dim + (long long)h * vdim + e);
+        }
+        out[idx] = v;
+    }
+}
+
+// out[t, h, :vdim] = in[t, h, :vdim] * sigmoid(g[t, h]) in 16-byte pieces of bfloat16
+__global__ void gate_heads_vec_kernel(uint4* __restrict__ out, const __nv_bfloat16* __restrict__ in, long long in_stride, int in_head,
+                                      const __nv_bfloat16* __restrict__ g, long long g_stride, int n_tokens, int n_heads, int vdim) {
+    const int vp = vdim / 8;
+    const long long total = (long long)n_tokens * n_heads * vp;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / (n_heads * vp)), j = (int)(idx - (long long)t * n_heads * vp), h = j / vp, e = (j - h * vp) * 8;
+        const float gate = 1.0f / (1.0f + expf(-__bfloat162float(g[(long long)t * g_stride + h])));
+        const uint4 raw = *reinterpret_cast<const uint4*>(in + (long long)t * in_stride + (long long)h * in_head + e);
+        const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint4 res;
+        __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __bfloat1622float2(hp[i]);
+            rp[i] = __floats2bfloat162_rn(v.x * gate, v.y * gate);
+        }
+        out[idx] = res;
+    }
+}
+
 // out[t, h, i] = in[t, h, i] * sigmoid(g[t, h]) for i < vdim: the output gate on the heads of an attention result.
 template <typename T>
 __global__ void gate_heads_kernel(T* __restrict__ out, const T* __restrict__ in, long long in_stride, int in_head,
@@ -153,6 +211,17 @@ __global__ void gate_heads_kernel(T* __restrict__ out, const T* __restrict__ in,
 // over k runs lane by lane in a fixed order and ends in a shuffle tree: it depends on k alone.
 constexpr int HL_ROWS = 8, HL_WARPS = 8;
 
+__device__ __forceinline__ void load_piece(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+__device__ __forceinline__ void load_piece(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(HL_WARPS * 32) heads_linear_kernel(HeadsLinearArgs a) {
     rdl_grid_wait();
@@ -166,11 +235,30 @@ __global__ void __launch_bounds__(HL_WARPS * 32) heads_linear_kernel(HeadsLinear
 #pragma unroll
     for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
     const int rows = min(HL_ROWS, a.n_tokens - t0);
-    for (int k = lane; k < a.k; k += 32) {
-        const float wv = to_float(w[k]);
+    const T* xb = (const T*)a.x + (long long)t0 * a.x_stride + (long long)h * a.x_head;
+    constexpr int N = 16 / (int)sizeof(T);       // values of a 16-byte piece
+    // 16-byte pieces where every row of w and x starts on such a boundary; which form runs depends on sizes and addresses, not on the row count
+    if (a.k % N == 0 && (((uintptr_t)a.w | (uintptr_t)a.x) & 15) == 0 && a.x_stride % N == 0 && a.x_head % N == 0) {
+        for (int k = lane * N; k < a.k; k += 32 * N) {
+            float wv[N];
+            load_piece(w + k, wv);
 #pragma unroll
-        for (int r = 0; r < HL_ROWS; ++r)
-            if (r < rows) acc[r] = fmaf(wv, to_float(((const T*)a.x)[(long long)(t0 + r) * a.x_stride + (long long)h * a.x_head + k]), acc[r]);
+            for (int r = 0; r < HL_ROWS; ++r) {
+                if (r < rows) {
+                    float xv[N];
+                    load_piece(xb + (long long)r * a.x_stride + k, xv);
+#pragma unroll
+                    for (int j2 = 0; j2 < N; ++j2) acc[r] = fmaf(wv[j2], xv[j2], acc[r]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < a.k; k += 32) {
+            const float wv = to_float(w[k]);
+#pragma unroll
+            for (int r = 0; r < HL_ROWS; ++r)
+                if (r < rows) acc[r] = fmaf(wv, to_float(xb[(long long)r * a.x_stride + k]), acc[r]);
+        }
     }
 #pragma unroll
     for (int r = 0; r < HL_ROWS; ++r) {
@@ -221,6 +309,23 @@ extern "C" int rdl_latent_assemble(void* out, int dtype, const void* rows, long 
     RDL_REQUIRE(rdl_valid_dtype(dtype), "latent_assemble: bad dtype %d", dtype);
     RDL_REQUIRE(out && rows && kv && latent && n_heads > 0 && pad >= dim + rot_dim && pad >= vdim, "latent_assemble: bad arguments");
     if (n_tokens == 0) return 0;
+    const int piece = dtype == RDL_BF16 ? 8 : 4;
+    if (dim % piece == 0 && rot_dim % piece == 0 && vdim % piece == 0 && pad % piece == 0 && kv_rank % piece == 0 && row_stride % piece == 0 &&
+        q_col % piece == 0 && (((uintptr_t)out | (uintptr_t)rows | (uintptr_t)kv | (uintptr_t)latent) & 15) == 0) {
+        const long long total = 3LL * n_heads * (pad / piece) * n_tokens;
+        const long long want = (total + 255) / 256;
+        const unsigned blocks = (unsigned)(want > (long long)rdl_sm_count() * 16 ? (long long)rdl_sm_count() * 16 : want);
+        if (dtype == RDL_BF16)
+            latent_assemble_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+                (uint4*)out, (const __nv_bfloat16*)rows, row_stride, q_col, (const __nv_bfloat16*)kv, (const __nv_bfloat16*)latent, n_tokens,
+                n_heads, dim, rot_dim, vdim, kv_rank, pad);
+        else
+            latent_assemble_vec_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)out, (const float*)rows, row_stride, q_col,
+                                                                                         (const float*)kv, (const float*)latent, n_tokens,
+                                                                                         n_heads, dim, rot_dim, vdim, kv_rank, pad);
+        RDL_CHECK_LAUNCH("latent_assemble");
+        return 0;
+    }
     if (dtype == RDL_BF16)
         latent_assemble_kernel<__nv_bfloat16><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
             (__nv_bfloat16*)out, (const __nv_bfloat16*)rows, row_stride, q_col, (const __nv_bfloat16*)kv, (const __nv_bfloat16*)latent,
@@ -238,6 +343,14 @@ extern "C" int rdl_gate_heads(void* out, int dtype, const void* in, long long in
     RDL_REQUIRE(rdl_valid_dtype(dtype), "gate_heads: bad dtype %d", dtype);
     RDL_REQUIRE(out && in && g && n_heads > 0 && vdim > 0 && in_head >= vdim, "gate_heads: bad arguments");
     if (n_tokens == 0) return 0;
+    if (dtype == RDL_BF16 && vdim % 8 == 0 && in_head % 8 == 0 && in_stride % 8 == 0 && (((uintptr_t)out | (uintptr_t)in) & 15) == 0) {
+        const long long want = ((long long)n_tokens * n_heads * (vdim / 8) + 255) / 256;
+        const unsigned blocks = (unsigned)(want > (long long)rdl_sm_count() * 16 ? (long long)rdl_sm_count() * 16 : want);
+        gate_heads_vec_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)out, (const __nv_bfloat16*)in, in_stride, in_head,
+                                                                         (const __nv_bfloat16*)g, g_stride, n_tokens, n_heads, vdim);
+        RDL_CHECK_LAUNCH("gate_heads");
+        return 0;
+    }
     if (dtype == RDL_BF16)
         gate_heads_kernel<__nv_bfloat16><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, in_stride, in_head,
                                                                                       (const __nv_bfloat16*)g, g_stride, n_heads, vdim);

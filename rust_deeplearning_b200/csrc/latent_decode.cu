@@ -265,29 +265,49 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
     }
 }
 
-// out[t, h, :kv_rank] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in rising order
-__global__ void latent_decode_merge_kernel(LatentDecodeArgs a, int head_rows) {
+// out[t, h, :kv_rank] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in rising order.  The splits' factors
+// are formed once (shared memory); the sums then read their terms with all loads in flight.
+constexpr int LD_MAX_SPLITS = 64;
+
+__global__ void __launch_bounds__(128) latent_decode_merge_kernel(LatentDecodeArgs a, int head_rows) {
+    __shared__ float factor[LD_MAX_SPLITS];
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     const int t = blockIdx.y, head = blockIdx.x;
     if (a.tok_pos[t] < 0) return;
-    const int r_dim = a.kv_rank;
-    const float* base = a.partial + (((long long)t * head_rows + head) * a.n_splits) * (r_dim + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, base[(long long)s * (r_dim + 2) + r_dim]);
-    float L = 0.f;
-    for (int s = 0; s < a.n_splits; ++s) {
-        const float m = base[(long long)s * (r_dim + 2) + r_dim];
-        if (m != -INFINITY) L += base[(long long)s * (r_dim + 2) + r_dim + 1] * exp2f(m - M);
+    const int r_dim = a.kv_rank, stride = r_dim + 2;
+    const float* base = a.partial + (((long long)t * head_rows + head) * a.n_splits) * stride;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int s = lane + 32 * i;
+            m[i] = s < a.n_splits ? base[(long long)s * stride + r_dim] : -INFINITY;
+        }
+        const float M = warp_max(fmaxf(m[0], m[1]));
+        float f[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) f[i] = m[i] == -INFINITY ? 0.f : exp2f(m[i] - M);
+        // the sum over the splits in rising order, by one lane (a shuffle tree would order it by the lane count)
+        factor[lane] = f[0];
+        factor[lane + 32] = f[1];
+        __syncwarp();
+        float L = 0.f;
+        if (lane == 0) {
+            for (int s = 0; s < a.n_splits; ++s) L += base[(long long)s * stride + r_dim + 1] * factor[s];
+        }
+        L = __shfl_sync(0xffffffffu, L, 0);
+        factor[lane] = f[0] / L;
+        factor[lane + 32] = f[1] / L;
     }
+    __syncthreads();
     __nv_bfloat16* dst = a.out + (long long)t * a.out_stride + (long long)head * a.width;
     for (int i = threadIdx.x; i < r_dim; i += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < a.n_splits; ++s) {
-            const float m = base[(long long)s * (r_dim + 2) + r_dim];
-            if (m != -INFINITY) acc += base[(long long)s * (r_dim + 2) + i] * exp2f(m - M);
-        }
-        dst[i] = __float2bfloat16_rn(acc / L);
+#pragma unroll 8
+        for (int s = 0; s < a.n_splits; ++s) acc = fmaf(base[(long long)s * stride + i], factor[s], acc);
+        dst[i] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -328,6 +348,7 @@ extern "C" int rdl_latent_decode(void* out, long long out_stride, const void* q,
     const int groups = (n_heads + LD_HEADS - 1) / LD_HEADS;
     const int tiles = (max_keys + LD_TILE - 1) / LD_TILE + 1;     // a run of max_keys positions can straddle one more tile
     if (n_splits > tiles) n_splits = tiles;
+    if (n_splits > LD_MAX_SPLITS) n_splits = LD_MAX_SPLITS;
     RDL_REQUIRE(scratch_bytes >= rdl_latent_decode_scratch_bytes(n_tokens, n_heads, kv_rank, n_splits) && (n_splits == 1 || scratch),
                 "latent_decode: scratch too small");
     LatentDecodeArgs a{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, out_stride, tok_seq, tok_pos, tables,

@@ -18,51 +18,80 @@
 
 namespace {
 
-// Router logits z[t, e] = W_r[e, :] . x[t, :] in float.  A block takes ROUTE_ROWS rows and 8 experts, a warp one
-// expert for all of the block's rows: a weight row is read once for them, lanes split k (16-byte pieces where the width
-// allows), and the sum of a (row, expert) ends in a shuffle tree: its order depends on the width alone.
-constexpr int ROUTE_ROWS = 8, ROUTE_WARPS = 8;
+// Router logits z[t, e] = W_r[e, :] . x[t, :] in float, two forms; in both a (row, expert) sum is formed in an order
+// that depends on the width alone.
+//   many rows: a block takes ROWS rows and 8 experts, a warp one expert for all of the block's rows (a weight row is
+//     read once for them), lanes split k;
+//   few rows (single-token steps): a block takes one expert and up to 8 rows, its 8 warps split k, so that every load of
+//     the sum is in flight at once; the warps' parts are added in a fixed order through shared memory.
+constexpr int ROUTE_WARPS = 8, ROUTE_FEW_ROWS = 8, ROUTE_MANY_ROWS = 32;
 
-template <typename T>
+// four consecutive values as floats (8- or 16-byte load)
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+template <typename T, int ROWS, bool SPLIT_K>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(const T* __restrict__ x, const float* __restrict__ w_router, int n_rows,
                                                                       int n_experts, int width, float* __restrict__ z) {
+    __shared__ float part[ROUTE_WARPS][ROWS];
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * ROUTE_ROWS, e = blockIdx.y * ROUTE_WARPS + warp;
-    if (e >= n_experts) return;
-    const int rows = min(ROUTE_ROWS, n_rows - t0);
-    const float* w = w_router + (long long)e * width;
-    float acc[ROUTE_ROWS];
+    const int t0 = blockIdx.x * ROWS;
+    const int e = SPLIT_K ? blockIdx.y : blockIdx.y * ROUTE_WARPS + warp;
+    const bool live = e < n_experts;
+    const int rows = min(ROWS, n_rows - t0);
+    const float* w = w_router + (long long)(live ? e : 0) * width;
+    float acc[ROWS];
 #pragma unroll
-    for (int r = 0; r < ROUTE_ROWS; ++r) acc[r] = 0.f;
-    if (width % 4 == 0 && ((uintptr_t)w & 15) == 0) {
-        for (int k = lane * 4; k < width; k += 128) {
-            const float4 wv = *reinterpret_cast<const float4*>(w + k);
+    for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+    // SPLIT_K: all threads of the block walk k together; else a warp walks k alone
+    const int first = SPLIT_K ? threadIdx.x : lane, stride = SPLIT_K ? ROUTE_WARPS * 32 : 32;
+    if (live) {
+        if (width % 4 == 0 && ((uintptr_t)w_router & 15) == 0 && ((uintptr_t)x & 15) == 0) {
+            for (int k = first * 4; k < width; k += stride * 4) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + k);
 #pragma unroll
-            for (int r = 0; r < ROUTE_ROWS; ++r) {
-                if (r < rows) {
-                    const T* row = x + (long long)(t0 + r) * width + k;
-                    acc[r] = fmaf(wv.x, to_float(row[0]), acc[r]);
-                    acc[r] = fmaf(wv.y, to_float(row[1]), acc[r]);
-                    acc[r] = fmaf(wv.z, to_float(row[2]), acc[r]);
-                    acc[r] = fmaf(wv.w, to_float(row[3]), acc[r]);
+                for (int r = 0; r < ROWS; ++r) {
+                    if (r < rows) {
+                        const float4 xv = load4(x + (long long)(t0 + r) * width + k);
+                        acc[r] = fmaf(wv.x, xv.x, acc[r]);
+                        acc[r] = fmaf(wv.y, xv.y, acc[r]);
+                        acc[r] = fmaf(wv.z, xv.z, acc[r]);
+                        acc[r] = fmaf(wv.w, xv.w, acc[r]);
+                    }
                 }
             }
-        }
-    } else {
-        for (int k = lane; k < width; k += 32) {
-            const float wv = w[k];
+        } else {
+            for (int k = first; k < width; k += stride) {
+                const float wv = w[k];
 #pragma unroll
-            for (int r = 0; r < ROUTE_ROWS; ++r)
-                if (r < rows) acc[r] = fmaf(wv, to_float(x[(long long)(t0 + r) * width + k]), acc[r]);
+                for (int r = 0; r < ROWS; ++r)
+                    if (r < rows) acc[r] = fmaf(wv, to_float(x[(long long)(t0 + r) * width + k]), acc[r]);
+            }
         }
     }
 #pragma unroll
-    for (int r = 0; r < ROUTE_ROWS; ++r) {
-        if (r >= rows) break;
-        const float v = warp_sum(acc[r]);
-        if (lane == 0) z[(long long)(t0 + r) * n_experts + e] = v;
+    for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
+    if (!SPLIT_K) {
+        if (live && lane == 0)
+            for (int r = 0; r < rows; ++r) z[(long long)(t0 + r) * n_experts + e] = acc[r];
+        return;
+    }
+    if (lane == 0)
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) part[warp][r] = acc[r];
+    __syncthreads();
+    if (threadIdx.x < rows) {
+        float v = 0.f;
+#pragma unroll
+        for (int wdx = 0; wdx < ROUTE_WARPS; ++wdx) v += part[wdx][threadIdx.x];
+        z[(long long)(t0 + threadIdx.x) * n_experts + e] = v;
     }
 }
 
@@ -353,13 +382,20 @@ extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, co
     RDL_REQUIRE(n_experts <= 1024, "moe_route: %d experts exceed the 1,024 the router kernels hold", n_experts);
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const dim3 grid((n_rows + ROUTE_ROWS - 1) / ROUTE_ROWS, (n_experts + ROUTE_WARPS - 1) / ROUTE_WARPS);
-    if (dtype == RDL_BF16)
-        RDL_CHECK_EX(rdl_launch(moe_logits_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), 0, st, (const __nv_bfloat16*)x, w_router, n_rows,
-                                n_experts, width, logits), "moe_route");
-    else
-        RDL_CHECK_EX(rdl_launch(moe_logits_kernel<float>, grid, dim3(ROUTE_WARPS * 32), 0, st, (const float*)x, w_router, n_rows, n_experts, width,
-                                logits), "moe_route");
+    // few rows: a block per expert with k split between its warps; many rows: 32 rows and 8 experts a block
+    const bool few = n_rows <= 64;
+    const dim3 block(ROUTE_WARPS * 32);
+    const dim3 grid = few ? dim3((n_rows + ROUTE_FEW_ROWS - 1) / ROUTE_FEW_ROWS, n_experts)
+                          : dim3((n_rows + ROUTE_MANY_ROWS - 1) / ROUTE_MANY_ROWS, (n_experts + ROUTE_WARPS - 1) / ROUTE_WARPS);
+    if (dtype == RDL_BF16) {
+        const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+        if (few) RDL_CHECK_EX(rdl_launch(moe_logits_kernel<__nv_bfloat16, ROUTE_FEW_ROWS, true>, grid, block, 0, st, xp, w_router, n_rows, n_experts, width, logits), "moe_route");
+        else RDL_CHECK_EX(rdl_launch(moe_logits_kernel<__nv_bfloat16, ROUTE_MANY_ROWS, false>, grid, block, 0, st, xp, w_router, n_rows, n_experts, width, logits), "moe_route");
+    } else {
+        const float* xp = (const float*)x;
+        if (few) RDL_CHECK_EX(rdl_launch(moe_logits_kernel<float, ROUTE_FEW_ROWS, true>, grid, block, 0, st, xp, w_router, n_rows, n_experts, width, logits), "moe_route");
+        else RDL_CHECK_EX(rdl_launch(moe_logits_kernel<float, ROUTE_MANY_ROWS, false>, grid, block, 0, st, xp, w_router, n_rows, n_experts, width, logits), "moe_route");
+    }
     const size_t smem = (size_t)TOPK_WARPS * 2 * n_experts * sizeof(float);
     RDL_CHECK_EX(rdl_launch(moe_topk_kernel, dim3((n_rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(TOPK_WARPS * 32), smem, st, (const float*)logits,
                             correction, n_rows, n_experts, top, sel, sel_w), "moe_route");

@@ -826,10 +826,10 @@ def latent_decode(q: torch.Tensor, b: AttentionBatch, pages: KVPages, *, n_heads
     out = torch.empty_like(q)
     groups = (n_heads + 15) // 16
     tiles = (max(b.max_keys, 1) + 63) // 64 + 1
-    # about two blocks per multiprocessor, a block per 64 keys at most
-    splits = max(1, min(tiles, (2 * sm_count(q.device.index or 0)) // max(1, b.n_tokens * groups)))
+    # one wave of blocks (a block of the widest rows fills a multiprocessor's shared memory), a block per 64 keys at most
+    splits = max(1, min(tiles, 64, sm_count(q.device.index or 0) // max(1, b.n_tokens * groups)))
     if n_splits is not None:
-        splits = max(1, min(tiles, n_splits))
+        splits = max(1, min(tiles, 64, n_splits))
     lib = library.load()
     need = lib.rdl_latent_decode_scratch_bytes(b.n_tokens, n_heads, kv_rank, splits)
     buf = None
