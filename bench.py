@@ -265,13 +265,14 @@ DESIGN_SIZES = {
 }
 
 
-def design_point(cfg, vocab, torch, rng, steps, warmup, prompt_len, batches):
-    """Prefill tokens/s (one prompt in one step, median of 5 after 3) and decode tokens/s at each batch."""
+def design_point(cfg, vocab, torch, rng, steps, warmup, prompt_len, batches, long_prompt=CONTEXT):
+    """Prefill tokens/s (one prompt in one step, median of 5 after 3; and one long prompt, median of 3 after 1) and decode
+    tokens/s at each batch."""
     import gc
     from rust_deeplearning_b200 import Engine, random_model
     from rust_deeplearning_b200.kernels import library
     model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
-    engine = Engine(model, max_tokens=max(batches) * (prompt_len + 256), max_seqs=max(batches), max_context=prompt_len + 256)
+    engine = Engine(model, max_tokens=max(batches) * (prompt_len + 256), max_seqs=max(batches), max_context=max(prompt_len + 256, long_prompt))
     prompt = [int(v) for v in rng.integers(0, vocab, size=prompt_len)]
     times = []
     launches = 0
@@ -290,6 +291,22 @@ def design_point(cfg, vocab, torch, rng, steps, warmup, prompt_len, batches):
             times.append(start.elapsed_time(stop))
     out = {"prefill_tokens": prompt_len, "prefill_ms": round(statistics.median(times), 3),
            "prefill_tok_s": round(prompt_len / (statistics.median(times) * 1e-3), 1), "prefill_launches": launches}
+    long_ids = [int(v) for v in rng.integers(0, vocab, size=long_prompt)]
+    times = []
+    for k in range(4):
+        slot = engine.new_sequence()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([slot], [long_ids], "last")
+        stop.record()
+        torch.cuda.synchronize()
+        engine.release(slot)
+        if k >= 1:
+            times.append(start.elapsed_time(stop))
+    out["prefill_long_tokens"] = long_prompt
+    out["prefill_long_ms"] = round(statistics.median(times), 3)
+    out["prefill_long_tok_s"] = round(long_prompt / (statistics.median(times) * 1e-3), 1)
     for b in batches:
         ms, n_launch, _ = decode_run(engine, b, steps, warmup, vocab, torch, rng, prompt_len)
         out[f"decode_b{b}_ms"] = round(ms, 4)

@@ -79,15 +79,6 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
     const int last_tile = min(p / LD_TILE, first_tile + a.tiles_per_split - 1);
     const int n_tiles = last_tile - first_tile + 1;               // may be <= 0: a split beyond this token's keys
 
-    // queries of this head group, swizzled by head row; heads beyond the last are zero
-    for (int i = threadIdx.x; i < LD_HEADS * chunks; i += LD_THREADS) {
-        const int h = i / chunks, c = i - h * chunks;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (hg * LD_HEADS + h < a.n_heads)
-            v = *reinterpret_cast<const uint4*>(a.q + (long long)t * a.q_stride + (long long)(hg * LD_HEADS + h) * width + c * 8);
-        *reinterpret_cast<uint4*>(q_s + h * row_bytes + (rdl_swizzled_chunk(h, c, chunks) << 4)) = v;
-    }
-
     auto load_tile = [&](int tile, int buf) {
         unsigned char* dst = k_s + buf * tile_bytes;
         const int pos0 = tile * LD_TILE;
@@ -117,6 +108,16 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
     const int n_pairs = a.kv_rank >> 4;                           // pairs of value tiles in all
 
     if (n_tiles > 0) load_tile(first_tile, 0);
+    // queries of this head group, swizzled by head row; heads beyond the last are zero (the first tile's copies are on
+    // their way meanwhile)
+    for (int i = threadIdx.x; i < LD_HEADS * chunks; i += LD_THREADS) {
+        const int h = i / chunks, c = i - h * chunks;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (hg * LD_HEADS + h < a.n_heads)
+            v = *reinterpret_cast<const uint4*>(a.q + (long long)t * a.q_stride + (long long)(hg * LD_HEADS + h) * width + c * 8);
+        *reinterpret_cast<uint4*>(q_s + h * row_bytes + (rdl_swizzled_chunk(h, c, chunks) << 4)) = v;
+    }
+
     for (int it = 0; it < n_tiles; ++it) {
         const int buf = it & 1;
         if (it + 1 < n_tiles) {
@@ -279,25 +280,26 @@ __global__ void __launch_bounds__(128) latent_decode_merge_kernel(LatentDecodeAr
     const float* base = a.partial + (((long long)t * head_rows + head) * a.n_splits) * stride;
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
-        float m[2];
+        float m[2], l[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int s = lane + 32 * i;
             m[i] = s < a.n_splits ? base[(long long)s * stride + r_dim] : -INFINITY;
+            l[i] = s < a.n_splits ? base[(long long)s * stride + r_dim + 1] : 0.f;
         }
         const float M = warp_max(fmaxf(m[0], m[1]));
         float f[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) f[i] = m[i] == -INFINITY ? 0.f : exp2f(m[i] - M);
-        // the sum over the splits in rising order, by one lane (a shuffle tree would order it by the lane count)
-        factor[lane] = f[0];
-        factor[lane + 32] = f[1];
+        // the sum over the splits in rising order, by one lane from shared memory (a shuffle tree would order it otherwise)
+        factor[lane] = l[0] * f[0];
+        factor[lane + 32] = l[1] * f[1];
         __syncwarp();
         float L = 0.f;
-        if (lane == 0) {
-            for (int s = 0; s < a.n_splits; ++s) L += base[(long long)s * stride + r_dim + 1] * factor[s];
-        }
+        if (lane == 0)
+            for (int s = 0; s < a.n_splits; ++s) L += factor[s];
         L = __shfl_sync(0xffffffffu, L, 0);
+        __syncwarp();
         factor[lane] = f[0] / L;
         factor[lane + 32] = f[1] / L;
     }

@@ -79,8 +79,11 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(const T* _
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
     if (!SPLIT_K) {
-        if (live && lane == 0)
-            for (int r = 0; r < rows; ++r) z[(long long)(t0 + r) * n_experts + e] = acc[r];
+        if (live && lane == 0) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (r < rows) z[(long long)(t0 + r) * n_experts + e] = acc[r];
+        }
         return;
     }
     if (lane == 0)

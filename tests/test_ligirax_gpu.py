@@ -370,3 +370,18 @@ def test_trace_replay_as_a_process(dtype, tmp_path):
     lh.assert_logits(read(2), np.stack([wa[27], wb[20]]), dtype, "step 2")
     lh.assert_logits(read(3), wa[28:29], dtype, "step 3")
     lh.assert_logits(read(4), wa[29:30], dtype, "step 4")
+
+
+def test_command_line_generates_with_a_ligirax_folder(capsys):
+    """The command line picks the architecture by config.json; its greedy tokens are the entry point's."""
+    import io
+    from rust_deeplearning_b200 import Generator, cli
+    name = "LC"
+    p = lh.prompt(name, 50, 12, "float32")
+    out = io.StringIO()
+    code = cli.main([lh.model_folder(name), "--prompt-ids", " ".join(map(str, p)), "--max-tokens", "6", "--temperature", "0",
+                     "--dtype", "float32", "--max-context", "64"], stdout=out)
+    assert code == 0
+    assert "arch=Ligirax" in capsys.readouterr().err
+    gen = Generator(lh.loaded_model(name, "float32"), max_batch=1, max_context=64).with_temperature(0.0)
+    assert [int(t) for t in out.getvalue().split()] == gen.generate(p, 6)[len(p):]
