@@ -132,7 +132,7 @@ def _parse_layer(entry, i, n_layers):
         m = entry["mixer"]
         rm = ConfigReader(m, "mixer")
         heads = rm.integer("heads", minimum=1)
-        dim = rm.integer("dim", minimum=0)
+        dim = rm.integer("dim", minimum=1)
         rot_dim = rm.integer("rot_dim", minimum=2)
         vdim = rm.integer("vdim", minimum=1)
         kv_rank = rm.integer("kv_rank", minimum=1)

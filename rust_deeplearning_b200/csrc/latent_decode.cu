@@ -3,9 +3,9 @@
 // One cached row [c | kr] per key serves every query head as key (all kv_rank + rot_dim values) and as value (its
 // first kv_rank values).  A block takes one token, one group of 16 query heads and one run of keys (a split):
 // the keys come into shared memory once, 64 at a time, and all 16 heads use them -
-//     S[16 heads x 64 keys] = Q K^T            mma.sync m16n8k16, bfloat16 operands, float sums; warp w takes keys 16 w ..
-//     online softmax in float (row maxima and sums exchanged between the four warps through shared memory)
-//     O[16 heads x kv_rank] += P V             warp w takes every fourth pair of 8-column tiles of the values
+//     S[16 heads x 64 keys] = Q K^T            mma.sync m16n8k16, bfloat16 operands, float sums; warp w takes keys 8 w ..
+//     online softmax in float (row maxima and sums exchanged between the eight warps through shared memory)
+//     O[16 heads x kv_rank] += P V             warp w takes every eighth pair of 8-column tiles of the values
 // Cache rows are copied as they lie (their 16-byte chunks XOR-swizzled by the row's place in its page), which is the
 // layout ldmatrix reads without bank conflicts; Q and P are kept in shared memory in the same manner.
 // Tiles are double-buffered with cp.async.  With one split the block writes the heads' results itself; with more,
@@ -18,7 +18,7 @@
 
 namespace {
 
-constexpr int LD_TILE = 64, LD_THREADS = 128, LD_HEADS = 16;
+constexpr int LD_TILE = 64, LD_WARPS = 8, LD_THREADS = LD_WARPS * 32, LD_HEADS = 16;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -54,16 +54,17 @@ struct LatentDecodeArgs {
     float* partial;                                  // [tokens][head groups * 16][splits][kv_rank + 2] (splits > 1)
 };
 
-// NP: pairs of 8-column value tiles a warp accumulates (kv_rank <= 64 NP)
+// NP: pairs of 8-column value tiles a warp accumulates (kv_rank <= 128 NP)
 template <int NP>
 __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int width = a.width, chunks = width >> 3, row_bytes = width * 2;
     unsigned char* q_s = smem;                                    // [16][width]
     unsigned char* p_s = q_s + LD_HEADS * row_bytes;              // [16][64]
-    float* wmax = (float*)(p_s + LD_HEADS * LD_TILE * 2);         // [4][16]
-    float* wsum = wmax + 4 * LD_HEADS;                            // [4][16]
-    unsigned char* k_s = (unsigned char*)(wsum + 4 * LD_HEADS);   // [2][64][width]
+    float* wmax = (float*)(p_s + LD_HEADS * LD_TILE * 2);         // [8][16]
+    float* wsum = wmax + LD_WARPS * LD_HEADS;                     // [8][16]
+    long long* key_off_all = (long long*)(wsum + LD_WARPS * LD_HEADS);   // [2][64] where each key's row starts in the cache; -1: not read
+    unsigned char* k_s = (unsigned char*)(key_off_all + 2 * LD_TILE);    // [2][64][width]
     const int tile_bytes = LD_TILE * row_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -79,18 +80,23 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
     const int last_tile = min(p / LD_TILE, first_tile + a.tiles_per_split - 1);
     const int n_tiles = last_tile - first_tile + 1;               // may be <= 0: a split beyond this token's keys
 
+    // A tile's copies: 64 threads look the rows up in the page list, then every warp copies rows as they lie (their
+    // chunks are swizzled already), a lane a 16-byte chunk; rows outside the token's keys are zero.
     auto load_tile = [&](int tile, int buf) {
         unsigned char* dst = k_s + buf * tile_bytes;
+        long long* key_off = key_off_all + buf * LD_TILE;         // per buffer: the call before may still be read by slower warps
         const int pos0 = tile * LD_TILE;
-        for (int i = threadIdx.x; i < LD_TILE * chunks; i += LD_THREADS) {
-            const int key = i / chunks, c = i - key * chunks;
-            const int pos = pos0 + key;
-            unsigned char* d = dst + key * row_bytes + (c << 4);
-            if (pos >= lo && pos <= p) {
-                const long long off = rdl_cache_offset(table, pos, a.page_size, a.ring_pages, 1, 0, width);
-                cp_async16(smem_addr(d), a.cache + off + c * 8);  // the row as it lies: its chunks are swizzled already
-            } else {
-                *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+        if (threadIdx.x < LD_TILE) {
+            const int pos = pos0 + threadIdx.x;
+            key_off[threadIdx.x] = (pos >= lo && pos <= p) ? rdl_cache_offset(table, pos, a.page_size, a.ring_pages, 1, 0, width) : -1;
+        }
+        __syncthreads();
+        for (int key = warp; key < LD_TILE; key += LD_WARPS) {
+            const long long off = key_off[key];
+            unsigned char* d = dst + key * row_bytes;
+            for (int c = lane; c < chunks; c += 32) {
+                if (off >= 0) cp_async16(smem_addr(d + (c << 4)), a.cache + off + c * 8);
+                else *reinterpret_cast<uint4*>(d + (c << 4)) = make_uint4(0, 0, 0, 0);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -129,35 +135,35 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
         __syncthreads();                                          // the tile (and, the first time, Q) is in shared memory
         const unsigned char* kt = k_s + buf * tile_bytes;
         const int pos0 = (first_tile + it) * LD_TILE;
-        // ---- S = Q K^T for this warp's 16 keys ----
-        float s[2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+        // ---- S = Q K^T for this warp's 8 keys; one load of K fragments serves two steps of 16 along the row ----
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
         {
             const int a_row = lane & 15, a_k = (lane >> 4) << 3;
-            const int b_key = warp * 16 + (lane & 7) + ((lane >> 4) << 3), b_k = ((lane >> 3) & 1) << 3;
+            const int b_key = warp * 8 + (lane & 7), b_k = (lane >> 3) << 3;
             const int b_sw = (pos0 + b_key) % a.page_size;        // the row's place in its page: what its chunks were swizzled by
-            for (int k0 = 0; k0 < width; k0 += 16) {
-                uint32_t af[4], bf[4];
-                ldsm_x4(smem_addr(q_s + a_row * row_bytes + swz(a_row, k0 + a_k, chunks)), af);
-                ldsm_x4(smem_addr(kt + b_key * row_bytes + swz(b_sw, k0 + b_k, chunks)), bf);
-                mma16816(s[0], af, bf[0], bf[1]);
-                mma16816(s[1], af, bf[2], bf[3]);
+            const unsigned char* q_row = q_s + a_row * row_bytes;
+            const unsigned char* k_row = kt + b_key * row_bytes;
+#pragma unroll 2
+            for (int k0 = 0; k0 < width; k0 += 32) {
+                uint32_t af[4], af2[4], bf[4];
+                const bool two = k0 + 16 < width;
+                // beyond the row's end (its last step of 16) the second half of the load reads the next row and is not used
+                ldsm_x4(smem_addr(k_row + swz(b_sw, k0 + b_k, chunks)), bf);
+                ldsm_x4(smem_addr(q_row + swz(a_row, k0 + a_k, chunks)), af);
+                if (two) ldsm_x4(smem_addr(q_row + swz(a_row, k0 + 16 + a_k, chunks)), af2);
+                mma16816(s, af, bf[0], bf[1]);
+                if (two) mma16816(s, af2, bf[2], bf[3]);
             }
         }
-        // ---- mask, row maxima over the four warps ----
+        // ---- mask, row maxima over the warps ----
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int pos = pos0 + warp * 16 + j * 8 + 2 * qd + (e & 1);
-                const float v = (pos >= lo && pos <= p) ? s[j][e] * a.scale_log2 : -INFINITY;
-                s[j][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
+        for (int e = 0; e < 4; ++e) {
+            const int pos = pos0 + warp * 8 + 2 * qd + (e & 1);
+            const float v = (pos >= lo && pos <= p) ? s[e] * a.scale_log2 : -INFINITY;
+            s[e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -169,25 +175,24 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int row = g + 8 * r;
-            const float tm = fmaxf(fmaxf(wmax[row], wmax[LD_HEADS + row]), fmaxf(wmax[2 * LD_HEADS + row], wmax[3 * LD_HEADS + row]));
+            float tm = wmax[row];
+#pragma unroll
+            for (int w = 1; w < LD_WARPS; ++w) tm = fmaxf(tm, wmax[w * LD_HEADS + row]);
             const float m_new = fmaxf(m_run[r], tm);
             m_use[r] = m_new == -INFINITY ? 0.f : m_new;
             corr[r] = exp2f(m_run[r] - m_use[r]);                 // 0 while nothing has been seen
             m_run[r] = m_new;
         }
         // ---- P = 2^(S - m), row sums, P into shared memory as bfloat16 ----
-        float sm[2] = {0.f, 0.f};
+        float sm[2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const float p0 = exp2f(s[j][2 * r] - m_use[r]), p1 = exp2f(s[j][2 * r + 1] - m_use[r]);
-                const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                // the sums are those of the rounded weights, which is what multiplies the values
-                sm[r] += __bfloat162float(pb.x) + __bfloat162float(pb.y);
-                const int row = g + 8 * r, col = warp * 16 + j * 8 + 2 * qd;
-                *reinterpret_cast<__nv_bfloat162*>(p_s + row * (LD_TILE * 2) + swz(row, col, LD_TILE / 8)) = pb;
-            }
+        for (int r = 0; r < 2; ++r) {
+            const float p0 = exp2f(s[2 * r] - m_use[r]), p1 = exp2f(s[2 * r + 1] - m_use[r]);
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            // the sums are those of the rounded weights, which is what multiplies the values
+            sm[r] = __bfloat162float(pb.x) + __bfloat162float(pb.y);
+            const int row = g + 8 * r, col = warp * 8 + 2 * qd;
+            *reinterpret_cast<__nv_bfloat162*>(p_s + row * (LD_TILE * 2) + swz(row, col, LD_TILE / 8)) = pb;
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -199,7 +204,10 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int row = g + 8 * r;
-            l_run[r] = l_run[r] * corr[r] + ((wsum[row] + wsum[LD_HEADS + row]) + (wsum[2 * LD_HEADS + row] + wsum[3 * LD_HEADS + row]));
+            float ts = 0.f;
+#pragma unroll
+            for (int w = 0; w < LD_WARPS; ++w) ts += wsum[w * LD_HEADS + row];      // a fixed order
+            l_run[r] = l_run[r] * corr[r] + ts;
         }
         // ---- O = O * corr + P V for this warp's value tiles ----
 #pragma unroll
@@ -220,7 +228,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
                 const int sw = (pos0 + key) % a.page_size;
 #pragma unroll
                 for (int i = 0; i < NP; ++i) {
-                    const int pair = warp + 4 * i;
+                    const int pair = warp + LD_WARPS * i;
                     if (pair < n_pairs) {
                         uint32_t vf[4];
                         ldsm_x4_t(smem_addr(kt + key * row_bytes + swz(sw, pair * 16 + v_n, chunks)), vf);
@@ -244,7 +252,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
             __nv_bfloat16* dst = a.out + (long long)t * a.out_stride + (long long)head * width;
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
-                const int pair = warp + 4 * i;
+                const int pair = warp + LD_WARPS * i;
                 if (pair >= n_pairs) continue;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
@@ -256,7 +264,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
             if (warp == 0 && qd == 0) { dst[r_dim] = m_run[r]; dst[r_dim + 1] = l_run[r]; }
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
-                const int pair = warp + 4 * i;
+                const int pair = warp + LD_WARPS * i;
                 if (pair >= n_pairs) continue;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
@@ -356,13 +364,14 @@ extern "C" int rdl_latent_decode(void* out, long long out_stride, const void* q,
     LatentDecodeArgs a{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, out_stride, tok_seq, tok_pos, tables,
                        table_width, page_size, ring_pages, n_heads, width, kv_rank, window, score_scale * 1.4426950408889634f,
                        (tiles + n_splits - 1) / n_splits, n_splits, (float*)scratch};
-    const size_t smem = (size_t)LD_HEADS * width * 2 + LD_HEADS * LD_TILE * 2 + 2 * 4 * LD_HEADS * sizeof(float) + 2 * (size_t)LD_TILE * width * 2;
+    const size_t smem = (size_t)LD_HEADS * width * 2 + LD_HEADS * LD_TILE * 2 + 2 * LD_WARPS * LD_HEADS * sizeof(float) + 2 * LD_TILE * sizeof(long long) +
+                        2 * (size_t)LD_TILE * width * 2 + 64;      // 64: a fragment load may reach past the last row's end
     const dim3 grid(n_splits, groups, n_tokens);
     cudaStream_t st = (cudaStream_t)stream;
     int e;
-    if (kv_rank <= 128) e = launch_latent_decode<2>(a, grid, smem, st);
-    else if (kv_rank <= 256) e = launch_latent_decode<4>(a, grid, smem, st);
-    else e = launch_latent_decode<8>(a, grid, smem, st);
+    if (kv_rank <= 128) e = launch_latent_decode<1>(a, grid, smem, st);
+    else if (kv_rank <= 256) e = launch_latent_decode<2>(a, grid, smem, st);
+    else e = launch_latent_decode<4>(a, grid, smem, st);
     if (e) return e;
     if (n_splits > 1)
         RDL_CHECK_EX(rdl_launch(latent_decode_merge_kernel, dim3(n_heads, n_tokens), dim3(128), 0, st, a, groups * LD_HEADS), "latent_decode_merge");

@@ -20,11 +20,11 @@ namespace {
 
 // Router logits z[t, e] = W_r[e, :] . x[t, :] in float, two forms; in both a (row, expert) sum is formed in an order
 // that depends on the width alone.
-//   many rows: a block takes ROWS rows and 8 experts, a warp one expert for all of the block's rows (a weight row is
+//   many rows: a block takes 16 rows and 8 experts, a warp one expert for all of the block's rows (a weight row is
 //     read once for them), lanes split k;
 //   few rows (single-token steps): a block takes one expert and up to 8 rows, its 8 warps split k, so that every load of
 //     the sum is in flight at once; the warps' parts are added in a fixed order through shared memory.
-constexpr int ROUTE_WARPS = 8, ROUTE_FEW_ROWS = 8, ROUTE_MANY_ROWS = 32;
+constexpr int ROUTE_WARPS = 8, ROUTE_FEW_ROWS = 8, ROUTE_MANY_ROWS = 16, ROUTE_CHUNK = 256;
 
 // four consecutive values as floats (8- or 16-byte load)
 __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
@@ -52,19 +52,49 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(const T* _
     for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
     // SPLIT_K: all threads of the block walk k together; else a warp walks k alone
     const int first = SPLIT_K ? threadIdx.x : lane, stride = SPLIT_K ? ROUTE_WARPS * 32 : 32;
-    if (live) {
-        if (width % 4 == 0 && ((uintptr_t)w_router & 15) == 0 && ((uintptr_t)x & 15) == 0) {
-            for (int k = first * 4; k < width; k += stride * 4) {
-                const float4 wv = *reinterpret_cast<const float4*>(w + k);
+    const bool pieces = width % 4 == 0 && ((uintptr_t)w_router & 15) == 0 && ((uintptr_t)x & 15) == 0;
+    if (!SPLIT_K && pieces) {
+        // The block's rows pass through shared memory, 256 values of each at a time, as floats: its eight warps read the
+        // same rows, and what one warp brought in would not wait in L1 for the others.  A lane still meets k in the order
+        // lane * 4 + {0, 128, 256, ...}.
+        __shared__ __align__(16) float xs[SPLIT_K ? 1 : ROWS][ROUTE_CHUNK];
+        for (int k0 = 0; k0 < width; k0 += ROUTE_CHUNK) {
+            for (int idx = threadIdx.x; idx < ROWS * (ROUTE_CHUNK / 4); idx += ROUTE_WARPS * 32) {
+                const int r = idx / (ROUTE_CHUNK / 4), kk = (idx - r * (ROUTE_CHUNK / 4)) * 4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < rows && k0 + kk < width) v = load4(x + (long long)(t0 + r) * width + k0 + kk);
+                *reinterpret_cast<float4*>(&xs[r][kk]) = v;
+            }
+            __syncthreads();
+            if (live) {
+                for (int kk = lane * 4; kk < ROUTE_CHUNK && k0 + kk < width; kk += 128) {
+                    const float4 wv = *reinterpret_cast<const float4*>(w + k0 + kk);
 #pragma unroll
-                for (int r = 0; r < ROWS; ++r) {
-                    if (r < rows) {
-                        const float4 xv = load4(x + (long long)(t0 + r) * width + k);
+                    for (int r = 0; r < ROWS; ++r) {
+                        const float4 xv = *reinterpret_cast<const float4*>(&xs[r][kk]);
                         acc[r] = fmaf(wv.x, xv.x, acc[r]);
                         acc[r] = fmaf(wv.y, xv.y, acc[r]);
                         acc[r] = fmaf(wv.z, xv.z, acc[r]);
                         acc[r] = fmaf(wv.w, xv.w, acc[r]);
                     }
+                }
+            }
+            __syncthreads();
+        }
+    } else if (live) {
+        if (pieces) {
+            for (int k = first * 4; k < width; k += stride * 4) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + k);
+                float4 xv[ROWS];                           // every row's piece is asked for before any is used
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    xv[r] = r < rows ? load4(x + (long long)(t0 + r) * width + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    acc[r] = fmaf(wv.x, xv[r].x, acc[r]);
+                    acc[r] = fmaf(wv.y, xv[r].y, acc[r]);
+                    acc[r] = fmaf(wv.z, xv[r].z, acc[r]);
+                    acc[r] = fmaf(wv.w, xv[r].w, acc[r]);
                 }
             }
         } else {
@@ -385,7 +415,7 @@ extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, co
     RDL_REQUIRE(n_experts <= 1024, "moe_route: %d experts exceed the 1,024 the router kernels hold", n_experts);
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    // few rows: a block per expert with k split between its warps; many rows: 32 rows and 8 experts a block
+    // few rows: a block per expert with k split between its warps; many rows: 16 rows and 8 experts a block
     const bool few = n_rows <= 64;
     const dim3 block(ROUTE_WARPS * 32);
     const dim3 grid = few ? dim3((n_rows + ROUTE_FEW_ROWS - 1) / ROUTE_FEW_ROWS, n_experts)

@@ -768,14 +768,21 @@ def latent_assemble(rows: torch.Tensor, q_col: int, kv: torch.Tensor, latent: to
     return out
 
 
-def gate_heads(x: torch.Tensor, head_stride: int, gate: torch.Tensor, n_heads: int, vdim: int) -> torch.Tensor:
-    """[tokens, n_heads * vdim] = x[t, h * head_stride + i] * sigmoid(gate[t, h]) for i < vdim; `gate` may be a
-    column slice of wider rows."""
-    _need(x.dim() == 2 and x.stride(1) == 1 and gate.dim() == 2 and gate.stride(1) == 1 and gate.dtype is x.dtype
-          and gate.shape[1] >= n_heads and x.shape[1] >= (n_heads - 1) * head_stride + vdim, "gate_heads: shapes do not fit")
-    T = x.shape[0]
+def gate_heads(x: torch.Tensor, head_stride: int, gate: torch.Tensor, n_heads: int, vdim: int,
+               row_stride: Optional[int] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+    """[tokens, n_heads * vdim] = x[t * row_stride + h * head_stride + i] * sigmoid(gate[t, h]) for i < vdim; `gate` may be
+    a column slice of wider rows.  By default x is [tokens, ...] and row_stride its row stride; with row_stride and n_rows
+    given x is any dense tensor addressed by the two strides (head-major results of a batched product, say)."""
+    _need(gate.dim() == 2 and gate.stride(1) == 1 and gate.dtype is x.dtype and gate.shape[1] >= n_heads, "gate_heads: bad gate")
+    if row_stride is None:
+        _need(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= (n_heads - 1) * head_stride + vdim, "gate_heads: shapes do not fit")
+        T, row_stride = x.shape[0], x.stride(0)
+    else:
+        _need(x.is_contiguous() and n_rows is not None and x.numel() >= (n_rows - 1) * row_stride + (n_heads - 1) * head_stride + vdim,
+              "gate_heads: the strides reach beyond the tensor")
+        T = n_rows
     out = torch.empty((T, n_heads * vdim), dtype=x.dtype, device=x.device)
-    library.check(library.load().rdl_gate_heads(_ptr(out), _dtype_code(out), _ptr(x), x.stride(0), head_stride, _ptr(gate), gate.stride(0),
+    library.check(library.load().rdl_gate_heads(_ptr(out), _dtype_code(out), _ptr(x), row_stride, head_stride, _ptr(gate), gate.stride(0),
                                                 T, n_heads, vdim, _stream(x)))
     return out
 

@@ -69,6 +69,7 @@ class LatentAttention:
         self.w_ukv = torch.cat([w_ukv, torch.zeros((w_ukv.shape[0], rd), dtype=w_ukv.dtype, device=w_ukv.device)], dim=1).contiguous()
         # absorbed form: per head W_uk[h]^T as [kv_rank, dim] and W_uv[h] as [vdim, kv_rank]
         self.w_uk_t = wuk.view(H, d, r).transpose(1, 2).contiguous()
+        self.w_uk_b = wuk.view(H, d, r)      # the same matrices as a batched product's second operand
         self.w_uv_h = wuv.view(H, vd, r).contiguous()
         self.w_o = wo
         # the size heads are padded to for the ordinary prefill kernels: their fast forms take multiples of 64 (tensor
@@ -121,7 +122,15 @@ class LatentAttention:
         # it comes after the attention (and after the runs that read this run's rows, if any).
         write_first = pages is not None and (batch.is_decode or not cache.is_ring or not batch.has_past)
         latent = ops.latent_prepare(rows, q_rot_out=qp, q_rot_col=r, q_rot_head=width, write=write_first, **prep)
-        ops.heads_linear(rows, 0, d + rd, self.w_uk_t, out=qp, out_col=0, out_head=width)
+        # the per-head products: the library's own kernel for few rows and in 32-bit; a batched library product where the
+        # bfloat16 products of that many rows go to the library too (`ops.SKINNY_MAX_ROWS`)
+        batched = bf16 and rows.shape[0] > ops.SKINNY_MAX_ROWS
+        T = rows.shape[0]
+        if batched:
+            q_un = rows.as_strided((H, T, d), (d + rd, rows.stride(0), 1))
+            qp.view(T, H, width)[:, :, :r].copy_(torch.bmm(q_un, self.w_uk_b).transpose(0, 1))
+        else:
+            ops.heads_linear(rows, 0, d + rd, self.w_uk_t, out=qp, out_col=0, out_head=width)
         common = dict(n_heads=H, n_kv_heads=1, head_dim=width, score_scale=self.score_scale, softcap=None, window=self.window)
         if batch.is_decode or (not cache.owns_kv and owner_rows is None):
             ab = batch.attention_batch("all", self.window)
@@ -149,7 +158,11 @@ class LatentAttention:
                     batch.deferred_writes[run] = write
                 else:
                     write()
-        o = ops.heads_linear(ctx, 0, width, self.w_uv_h, gate=gate)
+        if batched:
+            per_head = torch.bmm(ctx.as_strided((H, T, r), (width, ctx.stride(0), 1)), self.w_uv_h.transpose(1, 2))     # [H, T, vdim]
+            o = ops.gate_heads(per_head, T * vd, gate, H, vd, row_stride=vd, n_rows=T)
+        else:
+            o = ops.heads_linear(ctx, 0, width, self.w_uv_h, gate=gate)
         return ops.linear_branch(o, self.w_o, sink)
 
 
