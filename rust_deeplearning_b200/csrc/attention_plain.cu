@@ -18,9 +18,9 @@
 #include "api.h"
 #include "common.cuh"
 
-#define PLAIN_MAX_CHUNKS 16  // head_dim <= 512
+#define PLAIN_MAX_CHUNKS 32  // head_dim <= 1024 in the wide form (the rows of a latent cache are wider than ordinary heads); 16 otherwise
 
-template <typename T>
+template <typename T, int CHUNKS>
 __global__ void attention_plain_kernel(AttentionArgs a) {
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -37,9 +37,9 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
     const T* q = (const T*)a.q + (long long)t * a.q_stride + (long long)h * hd;
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
 
-    float acc[PLAIN_MAX_CHUNKS];
+    float acc[CHUNKS];
 #pragma unroll
-    for (int c = 0; c < PLAIN_MAX_CHUNKS; ++c) acc[c] = 0.f;
+    for (int c = 0; c < CHUNKS; ++c) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
 
     for (int jb = (lo / 32) * 32; jb <= p; jb += 32) {
@@ -72,7 +72,7 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
         l = l * corr + warp_sum(pj);
         m = m_new;
 #pragma unroll
-        for (int c = 0; c < PLAIN_MAX_CHUNKS; ++c) acc[c] *= corr;
+        for (int c = 0; c < CHUNKS; ++c) acc[c] *= corr;
         const unsigned long long vaddr = (unsigned long long)vp;
         for (int jj = 0; jj < 32; ++jj) {
             const int jk = jb + jj;
@@ -83,7 +83,7 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
             const int vsw = __shfl_sync(0xffffffffu, sw, jj);
             const T* vrow = (const T*)(((unsigned long long)hi32 << 32) | lo32);
 #pragma unroll
-            for (int c = 0; c < PLAIN_MAX_CHUNKS; ++c) {
+            for (int c = 0; c < CHUNKS; ++c) {
                 const int d = c * 32 + lane;
                 if (d < hd) acc[c] = fmaf(pw, to_float(vrow[vsw < 0 ? d : rdl_cache_col<T>(vsw, d, hd)]), acc[c]);
             }
@@ -92,7 +92,7 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
     T* o = (T*)a.out + (long long)t * a.out_stride + (long long)h * hd;
     const float inv = 1.0f / l;
 #pragma unroll
-    for (int c = 0; c < PLAIN_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < CHUNKS; ++c) {
         const int d = c * 32 + lane;
         if (d < hd) o[d] = from_float<T>(acc[c] * inv);
     }
@@ -125,10 +125,14 @@ extern "C" int rdl_attention_plain(const AttentionArgs* a, void* stream) {
     const int warps = 4;
     const long long items = (long long)a->n_tokens * a->n_heads;
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
-    if (a->dtype == RDL_BF16)
-        attention_plain_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(*a);
-    else
-        attention_plain_kernel<float><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(*a);
+    const bool wide = a->head_dim > 32 * 16;      // the accumulator of a head lives in registers: 16 or 32 values a lane
+    if (a->dtype == RDL_BF16) {
+        if (wide) attention_plain_kernel<__nv_bfloat16, PLAIN_MAX_CHUNKS><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(*a);
+        else attention_plain_kernel<__nv_bfloat16, 16><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(*a);
+    } else {
+        if (wide) attention_plain_kernel<float, PLAIN_MAX_CHUNKS><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(*a);
+        else attention_plain_kernel<float, 16><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(*a);
+    }
     RDL_CHECK_LAUNCH("attention_plain");
     return 0;
 }

@@ -149,6 +149,7 @@ def test_router_and_experts(dtype, rows, shape):
 @pytest.mark.parametrize("case", [
     # heads, kv_rank, rot_dim, page, window, splits
     (6, 32, 16, 16, 9, 1), (6, 32, 16, 16, 9, 3), (16, 96, 32, 64, 72, None), (20, 48, 16, 8, None, 2), (3, 448, 64, 64, 200, None),
+    (2, 512, 64, 64, 300, 4),
     (17, 256, 64, 32, None, 5), (1, 16, 16, 16, 64, 1)])
 def test_latent_decode_kernel_against_the_plain_kernel(case):
     """The tensor-core decode kernel of the absorbed form against the float kernel: pages in random order, sequences of
