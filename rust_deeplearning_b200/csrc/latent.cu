@@ -100,6 +100,95 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(LatentPrepar
     for (int i = threadIdx.x; i < width; i += LP_THREADS) dst[rdl_cache_col<T>(r, i, width)] = out[i];
 }
 
+// The same work in bfloat16 with 16-byte accesses, for interleaved pairs where every size and offset is a whole number of
+// 8-value chunks: a chunk of the rotated parts holds four whole pairs, a chunk of the latent goes to the rows and to its
+// (swizzled) place in the cache as soon as it is normed.  The sum of squares is formed chunk by chunk, then by the block's
+// fixed tree: its order depends on kv_rank alone.
+__device__ __forceinline__ uint4 rotate_chunk(const uint4 raw, const float* __restrict__ cs, const float* __restrict__ sn) {
+    const float4 c4 = *reinterpret_cast<const float4*>(cs), s4 = *reinterpret_cast<const float4*>(sn);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    uint4 out;
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h[i]);
+        o[i] = __floats2bfloat162_rn(v.x * c[i] - v.y * s[i], v.y * c[i] + v.x * s[i]);
+    }
+    return out;
+}
+
+__global__ void __launch_bounds__(LP_THREADS) latent_prepare_vec_kernel(LatentPrepareArgs a) {
+    __shared__ float red[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = a.tok_pos[t];
+    if (pos < 0) return;                       // a padding row of a fixed-size batch
+    typedef __nv_bfloat16 T;
+    T* row = (T*)a.rows + (long long)t * a.row_stride;
+    const int half = a.rot_n >> 1;
+    const float* cs = a.cos_t + (long long)pos * half;
+    const float* sn = a.sin_t + (long long)pos * half;
+    const int hq = a.dim + a.rot_dim, rc = a.rot_dim >> 3, rot_chunks = a.rot_n >> 3;
+    // queries: chunk c of head h's rotated part
+    for (int idx = threadIdx.x; idx < a.n_heads * rc; idx += LP_THREADS) {
+        const int h = idx / rc, c = idx - h * rc;
+        T* src = row + a.q_col + (long long)h * hq + a.dim + c * 8;
+        T* dst = a.q_rot_out ? (T*)a.q_rot_out + (long long)t * a.q_rot_stride + (long long)h * a.q_rot_head + c * 8 : src;
+        uint4 v = *reinterpret_cast<const uint4*>(src);
+        if (c < rot_chunks) v = rotate_chunk(v, cs + c * 4, sn + c * 4);
+        else if (dst == src) continue;
+        *reinterpret_cast<uint4*>(dst) = v;
+    }
+    if (a.latent_col < 0) return;              // a layer that reads another layer's latent rows
+    const T* lat = row + a.latent_col;
+    const int lc = a.kv_rank >> 3, width = a.kv_rank + a.rot_dim, chunks = width >> 3;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < lc; c += LP_THREADS) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(lat + c * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __bfloat1622float2(h[i]);
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)a.kv_rank + a.eps);
+    T* out = (T*)a.latent_out + (long long)t * width;
+    // where the row goes in the cache (in a ring a later token of this step may land on the same row: only the last writes)
+    T* cache_row = nullptr;
+    int r = 0;
+    if (a.do_write) {
+        const int seq = a.tok_seq[t];
+        if ((long long)pos + (long long)a.ring_pages * a.page_size >= (long long)a.seq_end[seq]) {
+            cache_row = (T*)a.cache + rdl_cache_offset(a.tables + (long long)seq * a.table_width, pos, a.page_size, a.ring_pages, 1, 0, width);
+            r = pos % a.page_size;
+        }
+    }
+    for (int c = threadIdx.x; c < chunks; c += LP_THREADS) {
+        uint4 v = *reinterpret_cast<const uint4*>(lat + c * 8);
+        if (c < lc) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            uint4 res;
+            __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 x = __bfloat1622float2(h[i]);
+                o[i] = __floats2bfloat162_rn(x.x * inv * rdl_load(a.norm_w, c * 8 + 2 * i, a.norm_w_dtype),
+                                             x.y * inv * rdl_load(a.norm_w, c * 8 + 2 * i + 1, a.norm_w_dtype));
+            }
+            v = res;
+        } else if (c - lc < rot_chunks) {
+            v = rotate_chunk(v, cs + (c - lc) * 4, sn + (c - lc) * 4);
+        }
+        *reinterpret_cast<uint4*>(out + c * 8) = v;
+        if (cache_row) *reinterpret_cast<uint4*>(cache_row + rdl_swizzled_chunk(r, c, chunks) * 8) = v;
+    }
+}
+
 // A step's latent rows [c | kr] into the cache, as a kernel of its own (a ring group's write that had to wait
 // for the readers of the rows it overwrites).
 template <typename T>
@@ -283,7 +372,14 @@ extern "C" int rdl_latent_prepare(const LatentPrepareArgs* a, void* stream) {
                                  a->ring_pages <= a->table_width), "latent_prepare: cache write without storage or with bad paging");
     if (a->n_tokens == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (a->dtype == RDL_BF16)
+    const bool chunked = a->dtype == RDL_BF16 && a->interleaved && a->rot_n % 8 == 0 && a->dim % 8 == 0 && a->rot_dim % 8 == 0 && a->kv_rank % 8 == 0 &&
+                         a->q_col % 8 == 0 && a->row_stride % 8 == 0 && ((uintptr_t)a->rows & 15) == 0 && (a->latent_col < 0 || a->latent_col % 8 == 0) &&
+                         (!a->q_rot_out || (((uintptr_t)a->q_rot_out & 15) == 0 && a->q_rot_stride % 8 == 0 && a->q_rot_head % 8 == 0)) &&
+                         (a->latent_col < 0 || ((uintptr_t)a->latent_out & 15) == 0) && (!a->do_write || ((uintptr_t)a->cache & 15) == 0) &&
+                         (a->rot_n == 0 || (((uintptr_t)a->cos_t | (uintptr_t)a->sin_t) & 15) == 0);
+    if (chunked)
+        RDL_CHECK_EX(rdl_launch(latent_prepare_vec_kernel, dim3(a->n_tokens), dim3(LP_THREADS), 0, st, *a), "latent_prepare");
+    else if (a->dtype == RDL_BF16)
         RDL_CHECK_EX(rdl_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(a->n_tokens), dim3(LP_THREADS), 0, st, *a), "latent_prepare");
     else
         RDL_CHECK_EX(rdl_launch(latent_prepare_kernel<float>, dim3(a->n_tokens), dim3(LP_THREADS), 0, st, *a), "latent_prepare");

@@ -35,15 +35,18 @@ def _close(got, want, dtype, what):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("interleaved", [True, False])
-def test_latent_prepare_norms_rotates_and_writes(dtype, interleaved):
+@pytest.mark.parametrize("sizes", [(3, 5, 12, 20, 2), (3, 8, 16, 24, 8)])
+def test_latent_prepare_norms_rotates_and_writes(dtype, interleaved, sizes):
     """The kernel between projection and attention against the plain norm and rotation, with rot.dims below rot_dim,
-    queries written in place and elsewhere, and the cache write read back through the page list."""
+    queries written elsewhere, and the cache write read back through the page list; sizes that are no whole number of
+    16-byte chunks, and sizes that are (the kernel's chunked form)."""
     from rust_deeplearning_b200.kernels import ops
     from rust_deeplearning_b200.parts.position import Rotary
     rng = np.random.default_rng(1)
-    H, d, rd, r, T, page = 3, 5, 12, 20, 9, 4
+    H, d, rd, r, extra = sizes
+    T, page = 9, 4
     rot = {"base": 50.0, "dims": 8, "scaling": {"factor": 3.0, "original": 8, "fast": 4.0, "slow": 0.5}}
-    width = H * (d + rd) + r + rd + 2
+    width = H * (d + rd) + r + rd + extra
     rows = rng.normal(size=(T, width))
     w = rng.normal(size=r) + 1.0
     pos = np.array([3, 4, 5, 6, 7, 8, 9, 10, 11], dtype=np.int32)
