@@ -8,7 +8,8 @@
 //     O[16 heads x kv_rank] += P V             warp w takes every eighth pair of 8-column tiles of the values
 // Cache rows are copied as they lie (their 16-byte chunks XOR-swizzled by the row's place in its page), which is the
 // layout ldmatrix reads without bank conflicts; Q and P are kept in shared memory in the same manner.
-// Tiles are double-buffered with cp.async.  With one split the block writes the heads' results itself; with more,
+// A block holds one tile at a time (cp.async); two blocks share a multiprocessor (rows of up to 640 values leave room for
+// both), so one computes while the other's copies travel.  With one split the block writes the heads' results itself; with more,
 // each split leaves (max, sum, unnormalised O) in scratch and a second kernel merges them in a fixed order.
 // Sizes: kv_rank + rot_dim a multiple of 16 up to 640, kv_rank a multiple of 16 up to 512, pages of a multiple of 8
 // positions; any number of heads.
@@ -54,18 +55,21 @@ struct LatentDecodeArgs {
     float* partial;                                  // [tokens][head groups * 16][splits][kv_rank + 2] (splits > 1)
 };
 
-// NP: pairs of 8-column value tiles a warp accumulates (kv_rank <= 128 NP)
-template <int NP>
-__global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeArgs a) {
+// byte offset of 16-byte chunk c of a row whose chunk count is a multiple of 8 (every group of eight is swizzled)
+__device__ __forceinline__ int swz_chunk(int key7, int c) { return (c ^ key7) << 4; }
+
+// NP: pairs of 8-column value tiles a warp accumulates (kv_rank <= 128 NP).  FULL: a row is a whole number of groups of
+// eight chunks (128 bytes), so every chunk is swizzled and its place is one XOR away.
+template <int NP, bool FULL>
+__global__ void __launch_bounds__(LD_THREADS, 2) latent_decode_kernel(LatentDecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int width = a.width, chunks = width >> 3, row_bytes = width * 2;
     unsigned char* q_s = smem;                                    // [16][width]
     unsigned char* p_s = q_s + LD_HEADS * row_bytes;              // [16][64]
     float* wmax = (float*)(p_s + LD_HEADS * LD_TILE * 2);         // [8][16]
     float* wsum = wmax + LD_WARPS * LD_HEADS;                     // [8][16]
-    long long* key_off_all = (long long*)(wsum + LD_WARPS * LD_HEADS);   // [2][64] where each key's row starts in the cache; -1: not read
-    unsigned char* k_s = (unsigned char*)(key_off_all + 2 * LD_TILE);    // [2][64][width]
-    const int tile_bytes = LD_TILE * row_bytes;
+    long long* key_off = (long long*)(wsum + LD_WARPS * LD_HEADS);   // [64] where each key's row starts in the cache; -1: not read
+    unsigned char* k_s = (unsigned char*)(key_off + LD_TILE);        // [64][width]: one tile; a second block on the multiprocessor computes while this one's copies travel
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, hg = blockIdx.y, t = blockIdx.z;
@@ -82,9 +86,8 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
 
     // A tile's copies: 64 threads look the rows up in the page list, then every warp copies rows as they lie (their
     // chunks are swizzled already), a lane a 16-byte chunk; rows outside the token's keys are zero.
-    auto load_tile = [&](int tile, int buf) {
-        unsigned char* dst = k_s + buf * tile_bytes;
-        long long* key_off = key_off_all + buf * LD_TILE;         // per buffer: the call before may still be read by slower warps
+    auto load_tile = [&](int tile) {
+        unsigned char* dst = k_s;
         const int pos0 = tile * LD_TILE;
         if (threadIdx.x < LD_TILE) {
             const int pos = pos0 + threadIdx.x;
@@ -93,10 +96,13 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
         __syncthreads();
         for (int key = warp; key < LD_TILE; key += LD_WARPS) {
             const long long off = key_off[key];
-            unsigned char* d = dst + key * row_bytes;
-            for (int c = lane; c < chunks; c += 32) {
-                if (off >= 0) cp_async16(smem_addr(d + (c << 4)), a.cache + off + c * 8);
-                else *reinterpret_cast<uint4*>(d + (c << 4)) = make_uint4(0, 0, 0, 0);
+            unsigned char* d = dst + key * row_bytes + (lane << 4);
+            if (off >= 0) {                                        // uniform over the warp
+                const unsigned char* src = (const unsigned char*)(a.cache + off) + (lane << 4);
+                uint32_t da = smem_addr(d);
+                for (int c = lane; c < chunks; c += 32, da += 512, src += 512) cp_async16(da, src);
+            } else {
+                for (int c = lane; c < chunks; c += 32, d += 512) *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -113,7 +119,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int n_pairs = a.kv_rank >> 4;                           // pairs of value tiles in all
 
-    if (n_tiles > 0) load_tile(first_tile, 0);
+    if (n_tiles > 0) load_tile(first_tile);
     // queries of this head group, swizzled by head row; heads beyond the last are zero (the first tile's copies are on
     // their way meanwhile)
     for (int i = threadIdx.x; i < LD_HEADS * chunks; i += LD_THREADS) {
@@ -125,15 +131,10 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
     }
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < n_tiles) {
-            load_tile(first_tile + it + 1, buf ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        if (it > 0) load_tile(first_tile + it);                   // the sync that ended the tile before has freed the buffer
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                          // the tile (and, the first time, Q) is in shared memory
-        const unsigned char* kt = k_s + buf * tile_bytes;
+        const unsigned char* kt = k_s;
         const int pos0 = (first_tile + it) * LD_TILE;
         // ---- S = Q K^T for this warp's 8 keys; one load of K fragments serves two steps of 16 along the row ----
         float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -141,19 +142,35 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
             const int a_row = lane & 15, a_k = (lane >> 4) << 3;
             const int b_key = warp * 8 + (lane & 7), b_k = (lane >> 3) << 3;
             const int b_sw = (pos0 + b_key) % a.page_size;        // the row's place in its page: what its chunks were swizzled by
-            const unsigned char* q_row = q_s + a_row * row_bytes;
-            const unsigned char* k_row = kt + b_key * row_bytes;
+            const uint32_t q_row = smem_addr(q_s + a_row * row_bytes), k_row = smem_addr(kt + b_key * row_bytes);
+            float s2[4] = {0.f, 0.f, 0.f, 0.f};                   // a second chain of sums: the steps alternate between the two
+            if (FULL) {
+                // chunk indices of this lane's fragment rows at k0 = 0; a step of 32 values is four chunks further
+                const int qc = a_k >> 3, kc = b_k >> 3, q7 = a_row & 7, k7 = b_sw & 7;
 #pragma unroll 2
-            for (int k0 = 0; k0 < width; k0 += 32) {
-                uint32_t af[4], af2[4], bf[4];
-                const bool two = k0 + 16 < width;
-                // beyond the row's end (its last step of 16) the second half of the load reads the next row and is not used
-                ldsm_x4(smem_addr(k_row + swz(b_sw, k0 + b_k, chunks)), bf);
-                ldsm_x4(smem_addr(q_row + swz(a_row, k0 + a_k, chunks)), af);
-                if (two) ldsm_x4(smem_addr(q_row + swz(a_row, k0 + 16 + a_k, chunks)), af2);
-                mma16816(s, af, bf[0], bf[1]);
-                if (two) mma16816(s, af2, bf[2], bf[3]);
+                for (int c0 = 0; c0 < chunks; c0 += 4) {
+                    uint32_t af[4], af2[4], bf[4];
+                    ldsm_x4(k_row + swz_chunk(k7, c0 + kc), bf);
+                    ldsm_x4(q_row + swz_chunk(q7, c0 + qc), af);
+                    ldsm_x4(q_row + swz_chunk(q7, c0 + 2 + qc), af2);
+                    mma16816(s, af, bf[0], bf[1]);
+                    mma16816(s2, af2, bf[2], bf[3]);
+                }
+            } else {
+#pragma unroll 2
+                for (int k0 = 0; k0 < width; k0 += 32) {
+                    uint32_t af[4], af2[4], bf[4];
+                    const bool two = k0 + 16 < width;
+                    // beyond the row's end (its last step of 16) the second half of the load reads the next row and is not used
+                    ldsm_x4(k_row + swz(b_sw, k0 + b_k, chunks), bf);
+                    ldsm_x4(q_row + swz(a_row, k0 + a_k, chunks), af);
+                    if (two) ldsm_x4(q_row + swz(a_row, k0 + 16 + a_k, chunks), af2);
+                    mma16816(s, af, bf[0], bf[1]);
+                    if (two) mma16816(s2, af2, bf[2], bf[3]);
+                }
             }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[e] += s2[e];
         }
         // ---- mask, row maxima over the warps ----
         float mx[2] = {-INFINITY, -INFINITY};
@@ -192,7 +209,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
             // the sums are those of the rounded weights, which is what multiplies the values
             sm[r] = __bfloat162float(pb.x) + __bfloat162float(pb.y);
             const int row = g + 8 * r, col = warp * 8 + 2 * qd;
-            *reinterpret_cast<__nv_bfloat162*>(p_s + row * (LD_TILE * 2) + swz(row, col, LD_TILE / 8)) = pb;
+            *reinterpret_cast<__nv_bfloat162*>(p_s + row * (LD_TILE * 2) + swz_chunk(row & 7, col >> 3) + ((col & 7) << 1)) = pb;
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -223,15 +240,16 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(LatentDecodeA
 #pragma unroll
             for (int kk = 0; kk < LD_TILE; kk += 16) {
                 uint32_t pf[4];
-                ldsm_x4(smem_addr(p_s + a_row * (LD_TILE * 2) + swz(a_row, kk + a_k, LD_TILE / 8)), pf);
+                ldsm_x4(smem_addr(p_s + a_row * (LD_TILE * 2)) + swz_chunk(a_row & 7, (kk + a_k) >> 3), pf);
                 const int key = kk + v_key;
                 const int sw = (pos0 + key) % a.page_size;
+                const uint32_t v_row = smem_addr(kt + key * row_bytes);
 #pragma unroll
                 for (int i = 0; i < NP; ++i) {
                     const int pair = warp + LD_WARPS * i;
                     if (pair < n_pairs) {
                         uint32_t vf[4];
-                        ldsm_x4_t(smem_addr(kt + key * row_bytes + swz(sw, pair * 16 + v_n, chunks)), vf);
+                        ldsm_x4_t(v_row + (FULL ? swz_chunk(sw & 7, pair * 2 + (v_n >> 3)) : swz(sw, pair * 16 + v_n, chunks)), vf);
                         mma16816(o[i][0], pf, vf[0], vf[1]);
                         mma16816(o[i][1], pf, vf[2], vf[3]);
                     }
@@ -321,15 +339,21 @@ __global__ void __launch_bounds__(128) latent_decode_merge_kernel(LatentDecodeAr
     }
 }
 
-template <int NP>
-int launch_latent_decode(const LatentDecodeArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
+template <int NP, bool FULL>
+int launch_latent_decode_form(const LatentDecodeArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
     static bool opted = false;
     if (!opted) {
-        RDL_CUDA(cudaFuncSetAttribute(latent_decode_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), "latent_decode");
+        RDL_CUDA(cudaFuncSetAttribute(latent_decode_kernel<NP, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), "latent_decode");
         opted = true;
     }
-    RDL_CHECK_EX(rdl_launch(latent_decode_kernel<NP>, grid, dim3(LD_THREADS), smem, st, a), "latent_decode");
+    RDL_CHECK_EX(rdl_launch(latent_decode_kernel<NP, FULL>, grid, dim3(LD_THREADS), smem, st, a), "latent_decode");
     return 0;
+}
+
+template <int NP>
+int launch_latent_decode(const LatentDecodeArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
+    // rows of a multiple of 64 values: every chunk swizzled, and a step of 32 values never leaves the row
+    return a.width % 64 == 0 ? launch_latent_decode_form<NP, true>(a, grid, smem, st) : launch_latent_decode_form<NP, false>(a, grid, smem, st);
 }
 
 }  // namespace
@@ -364,8 +388,8 @@ extern "C" int rdl_latent_decode(void* out, long long out_stride, const void* q,
     LatentDecodeArgs a{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, out_stride, tok_seq, tok_pos, tables,
                        table_width, page_size, ring_pages, n_heads, width, kv_rank, window, score_scale * 1.4426950408889634f,
                        (tiles + n_splits - 1) / n_splits, n_splits, (float*)scratch};
-    const size_t smem = (size_t)LD_HEADS * width * 2 + LD_HEADS * LD_TILE * 2 + 2 * LD_WARPS * LD_HEADS * sizeof(float) + 2 * LD_TILE * sizeof(long long) +
-                        2 * (size_t)LD_TILE * width * 2 + 64;      // 64: a fragment load may reach past the last row's end
+    const size_t smem = (size_t)LD_HEADS * width * 2 + LD_HEADS * LD_TILE * 2 + 2 * LD_WARPS * LD_HEADS * sizeof(float) + LD_TILE * sizeof(long long) +
+                        (size_t)LD_TILE * width * 2 + 64;          // 64: a fragment load may reach past the last row's end
     const dim3 grid(n_splits, groups, n_tokens);
     cudaStream_t st = (cudaStream_t)stream;
     int e;

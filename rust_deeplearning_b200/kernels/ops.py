@@ -833,8 +833,9 @@ def latent_decode(q: torch.Tensor, b: AttentionBatch, pages: KVPages, *, n_heads
     out = torch.empty_like(q)
     groups = (n_heads + 15) // 16
     tiles = (max(b.max_keys, 1) + 63) // 64 + 1
-    # one wave of blocks (a block of the widest rows fills a multiprocessor's shared memory), a block per 64 keys at most
-    splits = max(1, min(tiles, 64, sm_count(q.device.index or 0) // max(1, b.n_tokens * groups)))
+    # one wave of two blocks a multiprocessor (two blocks of the widest rows fit its shared memory), a block per 64 keys at most
+    splits = max(1, min(tiles, 64, (2 * sm_count(q.device.index or 0)) // max(1, b.n_tokens * groups)))
+    splits = min(splits, max(1, (tiles + 1) // 2))      # two tiles a block at least: the merge costs as much as a tile
     if n_splits is not None:
         splits = max(1, min(tiles, 64, n_splits))
     lib = library.load()
