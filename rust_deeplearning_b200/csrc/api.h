@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 13
+#define RDL_ABI_VERSION 14
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -64,6 +64,9 @@ typedef struct {
     // them, one token per sequence; the kernel rotates the query and key heads itself (float tables
     // [position][rotary_dim / 2]; rotary_dim 0: no rotation) and writes the new key and value rows to the cache
     const float* rope_cos; const float* rope_sin; int rotary_dim; int new_rows;
+    // optional: one float per query head, a logit without key or value that joins the softmax's denominator
+    // (exp(sinks[h]) counts once; it is neither scaled nor capped); NULL: none
+    const float* sinks;
     // filled in by the launcher: clock cycles after which a wait is given up, and the test's extra bytes
     long long wait_cycles; int test_extra_tx;
 } AttentionArgs;
@@ -100,6 +103,59 @@ int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_hea
                    const int* tok_seq, const int* tok_pos, int do_rope, int do_write,
                    void* k_cache, void* v_cache, const int* tables, int table_width, int page_size,
                    int ring_pages, const int* seq_end, void* stream);
+
+// Rotation, a norm of every query and key head, and the cache write, on packed rows whose stride may exceed their
+// heads: the first n_heads + 2 n_kv_heads heads of head_dim values each are query, key and value heads.  A query or
+// key head is rotated in float (the first rotary_dim values, half-split pairs; do_rope 0: not at all) and then, if
+// norm_eps > 0, divided by sqrt(sum of its squares / norm_dim + norm_eps) (norm_dim: the head's size before any zero
+// padding); it is rounded once, on the way back into the row and into the cache.
+int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                        int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq, const int* tok_pos,
+                        int do_rope, float norm_eps, int norm_dim, int do_write, void* k_cache, void* v_cache,
+                        const int* tables, int table_width, int page_size, int ring_pages, const int* seq_end, void* stream);
+
+// ---- forms of the residual stream and of gates (csrc/rownorm.cu) ----
+// Norm after the sum: res <- norm(alpha * res + branch) with norm(v) = v / sqrt(mean(v^2) + eps) * (w + off), in float;
+// y (optional) receives the same rows in y_dtype.
+int rdl_postnorm(float* res, const void* branch, int branch_dtype, float alpha, const void* w, int w_dtype, float eps,
+                 float off, void* y, int y_dtype, int n_rows, int width, void* stream);
+// out = c * (norm(a; wa) + norm(b; wb)), float result; a and b in `dtype`, both norms with eps and offset 0
+int rdl_norm_pair(float* out, const void* a, const void* b, int dtype, const void* wa, const void* wb, int w_dtype,
+                  float eps, float c, int n_rows, int width, void* stream);
+#define RDL_GATE_SIGMOID 0
+#define RDL_GATE_SILU 1
+// out[t, i] = x[t, i] * gate_act(g[t, i]) for i < width; x, g and out in `dtype`, each with a row stride of its own
+int rdl_gate_mul(void* out, long long out_stride, const void* x, long long x_stride, const void* g, long long g_stride,
+                 int dtype, int gate_act, int n_rows, int width, void* stream);
+// Float rows x [rows][groups * group] normed group by group (v / sqrt(mean(v^2) + eps), times w[column] if w is given),
+// times gate_act(g[t, column]) if g is given, written in out_dtype.
+int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int n_rows, int groups, int group, const void* w,
+                        int w_dtype, float eps, const void* g, long long g_stride, int g_dtype, int gate_act, void* stream);
+
+// ---- linear attention with a fixed decay per head (csrc/decay_attention.cu) ----
+// Per sequence and head, S_t = decay_h S_(t-1) + k_t v_t^T and o_t = S_t^T q_t, with S [dim][vdim] in float, kept per
+// slot between steps.  q, k and v are read from packed rows; before they enter the recurrence q and k may be rotated
+// (the first rot_n values, half-split pairs, float tables), q, k and v may go through SiLU, and k is multiplied by
+// k_scale - all in float.
+typedef struct {
+    int dtype;                                  // of the packed rows
+    int n_tokens, n_seqs, n_heads, dim, vdim;
+    const void* rows; long long row_stride;
+    int q_col, k_col, v_col;                    // heads lie one after another from each column
+    int silu;                                   // 1: q, k and v go through SiLU
+    float k_scale;
+    const float* cos_t; const float* sin_t; int rot_n;    // [positions][rot_n / 2]; rot_n 0: no rotation
+    const float* decay;                         // [heads]
+    const int* tok_pos;                         // [tokens]; -1 marks a padding row
+    const int* seq_start;                       // [seqs + 1]
+    const int* slots;                           // [seqs] row of `state` that belongs to each sequence
+    float* state;                               // [slots][heads][dim][vdim]
+    float* out;                                 // [tokens][heads * vdim]
+} DecayAttentionArgs;
+// token by token, float throughout: the 32-bit path, single-token steps, and the reference of the chunked kernel
+int rdl_decay_attention_scan(const DecayAttentionArgs* a, void* stream);
+// bfloat16 rows, many tokens: chunks of 64 tokens on tensor cores, the state in float between chunks
+int rdl_decay_attention_chunked(const DecayAttentionArgs* a, void* stream);
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float, plain FMA in a fixed order of k
 int rdl_gemm_f32(void* out, const void* x, const void* w, int m, int n, int k, void* stream);

@@ -469,6 +469,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             lsum = fmaf(wt, sm_l[w][h], lsum);
         }
         if (n_splits == 1) {
+            if (a.sinks) lsum += exp2f(a.sinks[g * G + h] * LOG2E - M);    // a logit without key or value
             const float inv = 1.0f / lsum;
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (long long)(g * G + h) * hd + d);
             o2[0] = __floats2bfloat162_rn(osum.x * inv, osum.y * inv);
@@ -532,6 +533,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             L = fmaf(wt, v.y, L);
         }
         L = warp_sum(L);
+        if (a.sinks) L += exp2f(a.sinks[g * G + h] * LOG2E - M);
         if (lane == 0) inv_s[h] = 1.0f / L;
     }
     __syncthreads();

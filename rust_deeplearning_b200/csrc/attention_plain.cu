@@ -9,6 +9,7 @@
 //   s_j = cap * tanh(s_j / cap)            if cap > 0    attention.rs:419-423
 //   keys kept: j <= p and (window == 0 or p - j < window)  ops.rs:905-922, :932-952
 //   a = softmax_j(s)                                      ops.rs:598-608
+//   (with sinks: the denominator also holds exp(sinks[h]); the reference has none)
 //   o_h = sum_j a_j v_g,j                                 attention.rs:442-446
 // (paths within rustml/; attention.rs = nn/main/src/core/attention.rs).  The window holds for
 // single-token steps too, which the reference's cached path skips (attention.rs:429).
@@ -90,6 +91,15 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
         }
     }
     T* o = (T*)a.out + (long long)t * a.out_stride + (long long)h * hd;
+    // a sink is a logit without key or value: it joins the denominator once, neither scaled nor capped
+    if (a.sinks) {
+        const float sink = a.sinks[h];
+        const float m_all = fmaxf(m, sink);
+        const float corr = expf(m - m_all);
+        l = l * corr + expf(sink - m_all);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) acc[c] *= corr;
+    }
     const float inv = 1.0f / l;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {

@@ -233,6 +233,11 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
 
     // ---- normalise and store ----
     const int r0 = warp * 16 + quad, r1 = r0 + 8;
+    if (a.sinks) {      // a logit without key or value joins each row's denominator (base-2 domain, like m and l)
+        const float sink = a.sinks[h] * LOG2E;
+        l0 += exp2f(sink - m0);
+        l1 += exp2f(sink - m1);
+    }
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
     __nv_bfloat16* out = (__nv_bfloat16*)a.out;
 #pragma unroll

@@ -116,6 +116,7 @@ struct TcAttnArgs {
     float score_scale, softcap;
     int window;
     int* status;
+    const float* sinks;
 };
 
 // DB: 64-column blocks of a head (head_dim / 64)
@@ -356,6 +357,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         // global memory are whole 16-byte chunks of consecutive addresses: thread -> row on the way in
         // (chunks swizzled by the row, no bank conflicts), thread -> chunk on the way out.
         if (ok) {
+            if (a.sinks && m_ref > -INFINITY) l += exp2_fast(a.sinks[h] * LOG2E - m_ref);   // a logit without key or value
             const float inv = 1.0f / l;
             unsigned char* srow = sQ + (size_t)r * (hd * 2);
 #pragma unroll
@@ -451,7 +453,7 @@ extern "C" int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_wi
     if (int e = make_map(&map_q, a->q, a->n_tokens, row_width, QM)) return e;
     if (int e = make_map(&map_kv, a->q, a->n_tokens, row_width, KN)) return e;
     TcAttnArgs t{a->out, a->out_stride, a->tile_seq, a->tile_q0, a->n_tiles, a->seq_start, a->n_heads, a->n_kv_heads, a->head_dim,
-                 a->score_scale, a->softcap, a->window, a->status};
+                 a->score_scale, a->softcap, a->window, a->status, a->sinks};
     const int smem = QM * a->head_dim * 2 + 4 * KN * a->head_dim * 2 + QM * 128 + 1024;
     dim3 grid(a->n_heads, a->n_tiles);
     switch (a->head_dim / 64) {

@@ -226,3 +226,105 @@ extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, i
     RDL_CHECK_EX(e, "rope_cache");
     return 0;
 }
+
+// Rotation, a root-mean-square norm of every query and key head, and the cache write in one pass over packed
+// rows with a stride of their own.  A warp takes a head: it rotates in float into its slice of shared memory,
+// sums the squares in a fixed order (lane by lane, then across the warp), scales, and rounds once on the way
+// back into the row and, for key heads, into the cache.  Value heads are copied to the cache as they are.
+template <typename T>
+__global__ void rope_norm_cache_kernel(T* __restrict__ rows, long long row_stride, int n_heads, int n_kv_heads, int head_dim,
+                                       int rotary_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                       const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, int do_rope,
+                                       float norm_eps, int norm_dim, int do_write, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                       const int* __restrict__ tables, int table_width, int page_size, int ring_pages,
+                                       const int* __restrict__ seq_end) {
+    extern __shared__ float head_buf[];      // [warps][head_dim]
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    if (pos < 0) return;  // a padding row of a fixed-size batch
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    float* buf = head_buf + (size_t)warp * head_dim;
+    bool write = do_write && n_kv_heads > 0;
+    const int seq = tok_seq[t];
+    // In a ring a later token of this step may land on the same row: only the last writer writes.
+    if (write && (long long)pos + (long long)ring_pages * page_size < (long long)seq_end[seq]) write = false;
+    const int r = pos % page_size;
+    const int half = do_rope ? rotary_dim >> 1 : 0;
+    const float* c = cos_t + (long long)pos * half;
+    const float* s = sin_t + (long long)pos * half;
+    const int total = n_heads + 2 * n_kv_heads;
+    for (int head = warp; head < total; head += n_warps) {
+        T* row = rows + (long long)t * row_stride + (long long)head * head_dim;
+        const bool is_q = head < n_heads, is_v = head >= n_heads + n_kv_heads;
+        T* dst = nullptr;
+        if (write && !is_q) {
+            const int kv_head = is_v ? head - n_heads - n_kv_heads : head - n_heads;
+            dst = (is_v ? v_cache : k_cache) +
+                  rdl_cache_offset(tables + (long long)seq * table_width, pos, page_size, ring_pages, n_kv_heads, kv_head, head_dim);
+        }
+        if (is_v) {
+            if (dst)
+                for (int i = lane; i < head_dim; i += 32) dst[rdl_cache_col<T>(r, i, head_dim)] = row[i];
+            continue;
+        }
+        float ss = 0.f;
+        for (int i = lane; i < half; i += 32) {
+            const float x1 = to_float(row[i]), x2 = to_float(row[i + half]);
+            const float cs = c[i], sn = s[i];
+            const float lo = x1 * cs - x2 * sn, hi = x2 * cs + x1 * sn;
+            buf[i] = lo;
+            buf[i + half] = hi;
+            ss = fmaf(lo, lo, ss);
+            ss = fmaf(hi, hi, ss);
+        }
+        for (int i = 2 * half + lane; i < head_dim; i += 32) {
+            const float x = to_float(row[i]);
+            buf[i] = x;
+            ss = fmaf(x, x, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = norm_eps > 0.f ? 1.0f / sqrtf(ss / (float)norm_dim + norm_eps) : 1.0f;
+        __syncwarp();
+        for (int i = lane; i < head_dim; i += 32) {
+            const T v = from_float<T>(buf[i] * inv);
+            row[i] = v;
+            if (dst) dst[rdl_cache_col<T>(r, i, head_dim)] = v;
+        }
+        __syncwarp();
+    }
+}
+
+extern "C" int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                   int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq,
+                                   const int* tok_pos, int do_rope, float norm_eps, int norm_dim, int do_write, void* k_cache,
+                                   void* v_cache, const int* tables, int table_width, int page_size, int ring_pages,
+                                   const int* seq_end, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(dtype), "rope_norm_cache: bad dtype %d", dtype);
+    RDL_REQUIRE(n_tokens >= 0 && n_heads >= 0 && n_kv_heads >= 0 && n_heads + n_kv_heads > 0 && head_dim > 0 && head_dim <= 4096,
+                "rope_norm_cache: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d", n_tokens, n_heads, n_kv_heads, head_dim);
+    RDL_REQUIRE(row_stride >= (long long)(n_heads + 2 * n_kv_heads) * head_dim, "rope_norm_cache: the row stride is below the heads' width");
+    RDL_REQUIRE(!do_rope || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim && cos_table && sin_table),
+                "rope_norm_cache: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    RDL_REQUIRE(norm_eps <= 0.f || (norm_dim > 0 && norm_dim <= head_dim), "rope_norm_cache: norm_dim %d must lie in 1..head_dim", norm_dim);
+    RDL_REQUIRE(tok_seq && tok_pos, "rope_norm_cache: missing batch description");
+    RDL_REQUIRE(!do_write || n_kv_heads == 0 ||
+                    (k_cache && v_cache && tables && seq_end && page_size > 0 && ring_pages > 0 && ring_pages <= table_width),
+                "rope_norm_cache: cache write needs storage, page tables and lengths");
+    if (n_tokens == 0) return 0;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * head_dim * sizeof(float);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == RDL_BF16)
+        e = rdl_launch(rope_norm_cache_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(warps * 32), smem, st, (__nv_bfloat16*)rows, row_stride,
+                       n_heads, n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, norm_eps, norm_dim,
+                       do_write, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tables, table_width, page_size, ring_pages, seq_end);
+    else
+        e = rdl_launch(rope_norm_cache_kernel<float>, dim3(n_tokens), dim3(warps * 32), smem, st, (float*)rows, row_stride, n_heads,
+                       n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, norm_eps, norm_dim, do_write,
+                       (float*)k_cache, (float*)v_cache, tables, table_width, page_size, ring_pages, seq_end);
+    RDL_CHECK_EX(e, "rope_norm_cache");
+    return 0;
+}

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 13
+ABI_VERSION = 14
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -172,6 +172,7 @@ class AttentionArgs(ctypes.Structure):
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_longlong),
         ("counter_bytes", ctypes.c_longlong), ("status", ctypes.c_void_p),
         ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p), ("rotary_dim", ctypes.c_int), ("new_rows", ctypes.c_int),
+        ("sinks", ctypes.c_void_p),
         ("wait_cycles", ctypes.c_longlong), ("test_extra_tx", ctypes.c_int),     # filled in by the launcher
     ]
 
@@ -236,6 +237,20 @@ class HeadsLinearArgs(ctypes.Structure):
     ]
 
 
+class DecayAttentionArgs(ctypes.Structure):
+    """One call of linear attention with a fixed decay per head (`csrc/api.h`)."""
+    _fields_ = [
+        ("dtype", ctypes.c_int), ("n_tokens", ctypes.c_int), ("n_seqs", ctypes.c_int), ("n_heads", ctypes.c_int),
+        ("dim", ctypes.c_int), ("vdim", ctypes.c_int),
+        ("rows", ctypes.c_void_p), ("row_stride", ctypes.c_longlong),
+        ("q_col", ctypes.c_int), ("k_col", ctypes.c_int), ("v_col", ctypes.c_int),
+        ("silu", ctypes.c_int), ("k_scale", ctypes.c_float),
+        ("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p), ("rot_n", ctypes.c_int),
+        ("decay", ctypes.c_void_p), ("tok_pos", ctypes.c_void_p), ("seq_start", ctypes.c_void_p), ("slots", ctypes.c_void_p),
+        ("state", ctypes.c_void_p), ("out", ctypes.c_void_p),
+    ]
+
+
 class SamplingArgs(ctypes.Structure):
     _fields_ = [("temperature", ctypes.c_float), ("top_k", ctypes.c_int), ("top_p", ctypes.c_float),
                 ("repetition_penalty", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
@@ -255,6 +270,13 @@ _SIGNATURES = {
     "rdl_residual_add": [_P, _P, _I, _LL, _P],
     "rdl_convert_rows": [_P, _I, _P, _I, _P, _I, _I, _P],
     "rdl_rope_cache": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
+    "rdl_rope_norm_cache": [_P, _LL, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _F, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
+    "rdl_postnorm": [_P, _P, _I, _F, _P, _I, _F, _F, _P, _I, _I, _I, _P],
+    "rdl_norm_pair": [_P, _P, _P, _I, _P, _P, _I, _F, _F, _I, _I, _P],
+    "rdl_gate_mul": [_P, _LL, _P, _LL, _P, _LL, _I, _I, _I, _I, _P],
+    "rdl_group_norm_gate": [_P, _I, _P, _I, _I, _I, _P, _I, _F, _P, _LL, _I, _I, _P],
+    "rdl_decay_attention_scan": [ctypes.POINTER(DecayAttentionArgs), _P],
+    "rdl_decay_attention_chunked": [ctypes.POINTER(DecayAttentionArgs), _P],
     "rdl_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     "rdl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "rdl_gemm_skinny_norm": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, ctypes.POINTER(DeferredNormArgs), _P, _P],

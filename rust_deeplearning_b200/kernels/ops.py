@@ -183,6 +183,70 @@ def convert_rows(x: torch.Tensor, out_dtype: torch.dtype, row_index: Optional[to
     return out
 
 
+def postnorm_(residual: torch.Tensor, branch: torch.Tensor, norm: NormParams, alpha: float,
+              out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """Norm after the sum, in place on the float32 stream: residual <- rms_norm(alpha * residual + branch; norm).
+    With out_dtype the new rows are also returned in that type (the next part's input)."""
+    _need(residual.dtype is torch.float32 and residual.is_contiguous() and residual.dim() == 2,
+          "postnorm_: the stream is a contiguous float32 [rows, width] tensor")
+    _need(branch.is_contiguous() and branch.shape == residual.shape, "postnorm_: the branch must have the stream's shape")
+    rows, width = residual.shape
+    _need(norm.weight.is_contiguous() and norm.weight.numel() == width, f"postnorm_: the norm's weight must hold {width} values")
+    y = torch.empty((rows, width), dtype=out_dtype, device=residual.device) if out_dtype is not None else None
+    library.check(library.load().rdl_postnorm(_ptr(residual), _ptr(branch), _dtype_code(branch), float(alpha), _ptr(norm.weight),
+                                              _dtype_code(norm.weight), float(norm.eps), float(norm.offset), _ptr(y),
+                                              _dtype_code(y) if y is not None else 0, rows, width, _stream(residual)))
+    return y
+
+
+def norm_pair(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, factor: float) -> torch.Tensor:
+    """float32 factor * (rms_norm(a; wa) + rms_norm(b; wb)), both norms with plain weights."""
+    _need(a.dim() == 2 and a.shape == b.shape and a.dtype is b.dtype and a.is_contiguous() and b.is_contiguous(),
+          "norm_pair: two contiguous tensors of one shape and type")
+    rows, width = a.shape
+    _need(wa.dtype is wb.dtype and wa.is_contiguous() and wb.is_contiguous() and wa.numel() == width and wb.numel() == width,
+          f"norm_pair: two weights of {width} values and one type")
+    out = torch.empty((rows, width), dtype=torch.float32, device=a.device)
+    library.check(library.load().rdl_norm_pair(_ptr(out), _ptr(a), _ptr(b), _dtype_code(a), _ptr(wa), _ptr(wb), _dtype_code(wa),
+                                               float(eps), float(factor), rows, width, _stream(a)))
+    return out
+
+
+GATES = {"sigmoid": 0, "silu": 1}     # element-wise output gates (`csrc/api.h`, RDL_GATE_*)
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, kind: str) -> torch.Tensor:
+    """x * gate_fn(gate), element by element, in float; x and gate may be column slices of wider rows."""
+    _need(kind in GATES, f"unknown gate '{kind}', known: {sorted(GATES)}")
+    _need(x.dim() == 2 and gate.shape == x.shape and gate.dtype is x.dtype and x.stride(1) == 1 and gate.stride(1) == 1,
+          "gate_mul: rows and gates of one shape and type")
+    out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    library.check(library.load().rdl_gate_mul(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0),
+                                              _dtype_code(x), GATES[kind], x.shape[0], x.shape[1], _stream(x)))
+    return out
+
+
+def group_norm_gate(x: torch.Tensor, groups: int, *, eps: float, weight: Optional[torch.Tensor] = None,
+                    gate: Optional[torch.Tensor] = None, gate_kind: str = "sigmoid",
+                    out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """float32 rows [rows, groups * n] normed group by group (v / sqrt(mean(v^2) + eps)), times weight[column] if
+    given, times gate_fn(gate[row, column]) if given (gate may be a column slice of wider rows); result in out_dtype."""
+    _need(x.dtype is torch.float32 and x.dim() == 2 and x.is_contiguous() and x.shape[1] % groups == 0,
+          "group_norm_gate: contiguous float32 rows whose width the groups divide")
+    _need(gate_kind in GATES, f"unknown gate '{gate_kind}', known: {sorted(GATES)}")
+    rows, width = x.shape
+    if weight is not None:
+        _need(weight.is_contiguous() and weight.numel() == width, f"group_norm_gate: the weight must hold {width} values")
+    if gate is not None:
+        _need(gate.dim() == 2 and tuple(gate.shape) == (rows, width) and gate.stride(1) == 1, "group_norm_gate: bad gate rows")
+    out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    library.check(library.load().rdl_group_norm_gate(
+        _ptr(out), _dtype_code(out), _ptr(x), rows, groups, width // groups, _ptr(weight),
+        _dtype_code(weight) if weight is not None else 0, float(eps), _ptr(gate), gate.stride(0) if gate is not None else 0,
+        _dtype_code(gate) if gate is not None else 0, GATES[gate_kind], _stream(x)))
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 # matrix products
 # ------------------------------------------------------------------------------------------
@@ -477,6 +541,40 @@ def rope_cache(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, 
     return qkv
 
 
+def rope_norm_cache(rows: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, *, tok_seq, tok_pos,
+                    cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, rotary_dim: int = 0,
+                    norm_eps: float = 0.0, norm_dim: Optional[int] = None, pages: Optional[KVPages] = None,
+                    seq_end: Optional[torch.Tensor] = None):
+    """In place on packed rows [tokens, >= (n_heads + 2 n_kv_heads) * head_dim] (the row stride may exceed the heads):
+    every query and key head is rotated by the tables (if given) and, with norm_eps > 0, divided by
+    sqrt(sum of squares / norm_dim + norm_eps), all in float and rounded once; key and value rows then go to the
+    cache (if `pages` is given).  norm_dim: the head's size without zero padding (default head_dim)."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[1] >= (n_heads + 2 * n_kv_heads) * head_dim,
+          "rope_norm_cache: packed rows narrower than the heads")
+    T = rows.shape[0]
+    _int32(tok_pos, "tok_pos", T)
+    _int32(tok_seq, "tok_seq", T)
+    do_rope = cos is not None
+    if do_rope:
+        _need(cos.dtype is torch.float32 and sin.dtype is torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+              and cos.shape == sin.shape and cos.shape[1] * 2 == rotary_dim, "rotary tables must be float32 [positions, rotary_dim/2]")
+    do_write = pages is not None and n_kv_heads > 0
+    if do_write:
+        _need(pages.k.dtype is rows.dtype and pages.v.dtype is rows.dtype, "cache dtype differs from the activations'")
+        _need(tuple(pages.k.shape[1:]) == (n_kv_heads, pages.page_size, head_dim) and pages.k.is_contiguous()
+              and pages.v.is_contiguous() and pages.v.shape == pages.k.shape, "cache storage has the wrong shape")
+        _int32(pages.tables, "page tables")
+        _int32(seq_end, "seq_end")
+    library.check(library.load().rdl_rope_norm_cache(
+        _ptr(rows), rows.stride(0), _dtype_code(rows), T, n_heads, n_kv_heads, head_dim, rotary_dim if do_rope else 0,
+        _ptr(cos), _ptr(sin), _ptr(tok_seq), _ptr(tok_pos), int(do_rope), float(norm_eps), int(norm_dim or head_dim),
+        int(do_write), _ptr(pages.k) if do_write else None, _ptr(pages.v) if do_write else None,
+        _ptr(pages.tables) if do_write else None, pages.tables.shape[1] if do_write else 0,
+        pages.page_size if do_write else 0, pages.ring_pages if do_write else 0,
+        _ptr(seq_end) if do_write else None, _stream(rows)))
+    return rows
+
+
 PREFILL_QUERY_TILE = 64    # query rows of a tile in the lists the prefill attention kernels take
 
 
@@ -536,7 +634,8 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
               head_dim: int, score_scale: float, softcap: Optional[float], window: Optional[int],
               new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
               scratch=None, keys_per_split: Optional[int] = None, status: Optional[torch.Tensor] = None,
-              rotate_and_write: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]] = None):
+              rotate_and_write: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]] = None,
+              sinks: Optional[torch.Tensor] = None):
     """Attention of the step's tokens over cache and new rows.
 
     q: [tokens, >= n_heads * head_dim] rows whose first n_heads * head_dim values are the (rotated)
@@ -554,6 +653,8 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     the query and key heads by the float32 tables [positions, rotary_dim / 2] (None, None, 0: no
     rotation), writes the new key and value rows into the cache and attends over the cache including
     them.  The packed rows themselves stay as they are.
+    sinks: float32 [n_heads] - a logit per head without key or value whose exponential joins the softmax's
+    denominator once (neither scaled nor capped).
     Returns [tokens, n_heads * head_dim] in the dtype of q."""
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim, "attention: bad query rows")
     T = q.shape[0]
@@ -571,6 +672,10 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
                         head_dim, score_scale, softcap, window)
     if pages is not None:
         _need(pages.k.dtype is q.dtype, "attention: cache dtype differs from the activations'")
+    if sinks is not None:
+        _need(sinks.dtype is torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads and sinks.device == q.device,
+              "attention: sinks must be float32 [n_heads]")
+        a.sinks = sinks.data_ptr()
     fast_ok = q.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
     if kind == "auto":
         kind = "prefill" if fast_ok and b.n_tiles > 0 else "plain"
@@ -951,3 +1056,64 @@ def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param:
             and w_gate_up.shape[1] % 16 == 0 and x.is_contiguous() and x.data_ptr() % 16 == 0):
         return moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)
     return moe_experts_few(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)
+
+
+# ------------------------------------------------------------------------------------------
+# linear attention with a fixed decay per head
+# ------------------------------------------------------------------------------------------
+
+DECAY_CHUNKED_MIN_TOKENS = 64    # from this many rows on a bfloat16 step takes the chunked tensor-core kernel
+DECAY_CHUNKED = os.environ.get("RDL_DECAY_ATTENTION", "scan") != "scan"     # "scan": token by token everywhere, for comparison
+
+
+def decay_attention_chunked_ok(dtype, dim: int, vdim: int) -> bool:
+    """Whether the chunked kernel takes these head sizes."""
+    return dtype is torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+
+
+def decay_attention(rows: torch.Tensor, *, q_col: int, k_col: int, v_col: int, n_heads: int, dim: int, vdim: int,
+                    decay: torch.Tensor, state: torch.Tensor, tok_pos: torch.Tensor, seq_start: torch.Tensor,
+                    slots: torch.Tensor, n_seqs: int, silu: bool = False, k_scale: float = 1.0,
+                    cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, rot_n: int = 0,
+                    kind: str = "auto") -> torch.Tensor:
+    """Per sequence and head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's packed rows, from and
+    into `state` (float32 [slots, n_heads, dim, vdim], the row of a sequence given by `slots`).  q, k and v are read
+    from `rows` at the given columns (heads one after another); on the way into the recurrence q and k are rotated
+    (the first rot_n values, half-split pairs, float32 tables [positions, rot_n / 2]), q, k and v go through SiLU
+    (silu) and k is multiplied by k_scale, all in float.  Returns float32 [tokens, n_heads * vdim].
+    kind: "scan" (token by token, float), "chunked" (bfloat16 rows, tensor cores), "auto"."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1, "decay_attention: packed rows")
+    T = rows.shape[0]
+    _need(rows.shape[1] >= max(q_col + n_heads * dim, k_col + n_heads * dim, v_col + n_heads * vdim),
+          "decay_attention: the rows are narrower than the heads")
+    _need(decay.dtype is torch.float32 and decay.is_contiguous() and decay.numel() == n_heads, "decay_attention: float32 decay [heads]")
+    _need(state.dtype is torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (n_heads, dim, vdim),
+          "decay_attention: the state must be float32 [slots, heads, dim, vdim]")
+    _int32(tok_pos, "tok_pos", T)
+    _int32(seq_start, "seq_start", n_seqs + 1)
+    _int32(slots, "slots", n_seqs)
+    if rot_n:
+        _need(cos is not None and cos.dtype is torch.float32 and sin.dtype is torch.float32 and cos.is_contiguous()
+              and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[1] * 2 == rot_n,
+              "rotary tables must be float32 [positions, rot_n / 2]")
+    out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=rows.device)
+    a = library.DecayAttentionArgs()
+    a.dtype, a.n_tokens, a.n_seqs, a.n_heads, a.dim, a.vdim = _dtype_code(rows), T, n_seqs, n_heads, dim, vdim
+    a.rows, a.row_stride = rows.data_ptr(), rows.stride(0)
+    a.q_col, a.k_col, a.v_col = q_col, k_col, v_col
+    a.silu, a.k_scale = int(silu), float(k_scale)
+    if rot_n:
+        a.cos_t, a.sin_t, a.rot_n = cos.data_ptr(), sin.data_ptr(), rot_n
+    a.decay, a.tok_pos, a.seq_start, a.slots = decay.data_ptr(), tok_pos.data_ptr(), seq_start.data_ptr(), slots.data_ptr()
+    a.state, a.out = state.data_ptr(), out.data_ptr()
+    if kind == "auto":
+        kind = "chunked" if (DECAY_CHUNKED and T >= DECAY_CHUNKED_MIN_TOKENS and decay_attention_chunked_ok(rows.dtype, dim, vdim)) else "scan"
+    lib = library.load()
+    if kind == "scan":
+        library.check(lib.rdl_decay_attention_scan(ctypes.byref(a), _stream(rows)))
+    elif kind == "chunked":
+        _need(decay_attention_chunked_ok(rows.dtype, dim, vdim), "decay_attention: the chunked kernel takes bfloat16 heads of 16..128 values in steps of 16")
+        library.check(lib.rdl_decay_attention_chunked(ctypes.byref(a), _stream(rows)))
+    else:
+        raise KernelError(f"decay_attention: unknown kind '{kind}'")
+    return out

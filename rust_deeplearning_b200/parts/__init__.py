@@ -1,2 +1,3 @@
 """Parts of a model.  Importing the package registers the built-in kinds."""
-from . import attention, feed_forward, latent_attention, model, norm, position, routed_experts  # noqa: F401
+from . import (attention, decay_attention, feed_forward, latent_attention, mixer_pair, model, norm, position,  # noqa: F401
+               routed_experts)

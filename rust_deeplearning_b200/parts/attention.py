@@ -10,6 +10,17 @@ Interface of a mixer:
   needs() -> (KVRequirement | None, StateRequirement | None)  what it keeps per sequence
   forward(x [rows, hidden] normed, batch: StepBatch, cache: RunCache, run: int) -> [rows, hidden]
 `cache.owns_kv` False means this run reads the keys and values another run wrote.
+
+Optional parameters, for designs that have them (the reference's attention has none of these):
+  qk_norm_eps  after rotation every query and key head is divided by its root mean square (no weight), in float
+  sinks        a learned logit per query head without key or value: exp(sink_h) joins the softmax's denominator once
+  gate         "sigmoid": the concatenated heads are multiplied element by element by sigmoid(W_g x) before W_o
+  value_dim    values of another size than keys
+With any of them the mixer makes q, k, v and the gate's logits in one product and takes `ops.rope_norm_cache`
+(rotation, head norm and cache write in one pass, rounded once) in place of `ops.rope_cache`.  Keys and values of
+different sizes share the attention kernels by zero padding: the heads of q, k, v and of the gate are all laid out
+with max(head_dim, value_dim) values, the padding made by zero rows of the product's matrix (and zero columns of
+W_o), so that scores and outputs are unchanged and no kernel needs to know.
 Optional offers for the split form of the norms around few-row products (`parts/norm.py`):
 `takes_deferred_rows` (x may be `ops.DeferredRows`) and `delivers_branch` (forward takes `sink`).
 """
@@ -30,9 +41,15 @@ class Attention:
     query_tile_rows = ops.PREFILL_QUERY_TILE
 
     def __init__(self, *, hidden_size, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, position,
-                 wq, wk, wv, wo):
+                 wq, wk, wv, wo, value_dim=None, qk_norm_eps=None, sinks=None, gate=None, wg=None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
+        value_dim = head_dim if value_dim is None else value_dim
+        self.extended = (value_dim != head_dim or qk_norm_eps is not None or sinks is not None or gate is not None)
+        if self.extended:
+            self._init_extended(hidden_size, n_heads, n_kv_heads, head_dim, value_dim, score_scale, softcap, window, position,
+                                wq, wk, wv, wo, qk_norm_eps, sinks, gate, wg)
+            return
         if wv.shape[0] != wk.shape[0]:
             raise ValueError("this attention's kernels take key and value rows of one size")
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
@@ -44,6 +61,81 @@ class Attention:
         self.w_o = wo
         self.q_width = n_heads * head_dim
         self.kv_width = n_kv_heads * head_dim
+
+    def _init_extended(self, hidden_size, n_heads, n_kv_heads, head_dim, value_dim, score_scale, softcap, window, position,
+                       wq, wk, wv, wo, qk_norm_eps, sinks, gate, wg):
+        if gate not in (None, "sigmoid", "silu") or (gate is None) != (wg is None):
+            raise ValueError("attention: gate is None, 'sigmoid' or 'silu' and comes with its matrix")
+        if sinks is not None and sinks.numel() != n_heads:
+            raise ValueError(f"attention: {sinks.numel()} sinks for {n_heads} heads")
+        D = max(head_dim, value_dim)          # the size all heads are laid out with
+
+        def heads(w, n, d):                   # [n * d, in] -> [n * D, in], every head's rows padded with zero rows
+            if d == D:
+                return w
+            out = torch.zeros((n, D, w.shape[1]), dtype=w.dtype, device=w.device)
+            out[:, :d] = w.view(n, d, w.shape[1])
+            return out.view(n * D, w.shape[1])
+
+        parts = [heads(wq, n_heads, head_dim), heads(wk, n_kv_heads, head_dim), heads(wv, n_kv_heads, value_dim)]
+        if wg is not None:
+            parts.append(heads(wg, n_heads, value_dim))
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        if value_dim == D:
+            self.w_o = wo
+        else:                                 # zero columns under the padding of every head's output
+            w = torch.zeros((wo.shape[0], n_heads, D), dtype=wo.dtype, device=wo.device)
+            w[:, :, :value_dim] = wo.view(wo.shape[0], n_heads, value_dim)
+            self.w_o = w.view(wo.shape[0], n_heads * D).contiguous()
+        self.hidden_size, self.n_heads, self.n_kv_heads = hidden_size, n_heads, n_kv_heads
+        self.head_dim, self.true_head_dim, self.value_dim = D, head_dim, value_dim
+        self.score_scale, self.softcap, self.window, self.position = float(score_scale), softcap, window, position
+        self.qk_norm_eps = float(qk_norm_eps) if qk_norm_eps is not None else 0.0
+        self.sinks = sinks.to(torch.float32).contiguous() if sinks is not None else None
+        self.gate = gate
+        self.q_width, self.kv_width = n_heads * D, n_kv_heads * D
+        self.g_col = self.q_width + 2 * self.kv_width
+        self.takes_deferred_rows = False      # the rows are rotated and normed in place: a tensor is needed
+        self.delivers_branch = False
+
+    def _forward_extended(self, x, batch, cache: RunCache):
+        """q, k, v and the gate in one product; rotation, head norm and cache write in one pass; attention with the
+        sinks; the gate; the output product."""
+        if not cache.owns_kv:
+            raise ValueError("attention: a run with head norms, sinks or an output gate keeps keys and values of its own")
+        nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        pages = self._pages(batch, cache)
+        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
+        fast_decode = fast and nh // nkv <= 8 and cache.page_size % 16 == 0 and cache.page_size <= 64
+        common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, score_scale=self.score_scale, softcap=self.softcap,
+                      window=self.window, sinks=self.sinks, status=batch.status)
+        tables, rotary_dim = self._rotary_tables()
+        if self.position is not None and tables is None:
+            raise ValueError("attention: with head norms the position part must offer tables()")
+        prep = dict(tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, cos=tables[0] if tables else None,
+                    sin=tables[1] if tables else None, rotary_dim=rotary_dim, norm_eps=self.qk_norm_eps,
+                    norm_dim=self.true_head_dim, seq_end=batch.seq_end)
+        rows = ops.linear(x, self.w_qkv)
+        if batch.is_decode:
+            ops.rope_norm_cache(rows, nh, nkv, hd, pages=pages, **prep)
+            ab = batch.attention_batch("all", self.window)
+            ctx = ops.attention(rows, ab, pages, kind="decode" if fast_decode else "plain",
+                                scratch=lambda n: batch.scratch_buffer("decode", n), **common)
+        else:
+            # in a ring the write may overwrite rows of earlier steps that this step's early queries still need
+            write_first = pages is not None and (not cache.is_ring or not batch.has_past)
+            ops.rope_norm_cache(rows, nh, nkv, hd, pages=pages if write_first else None, **prep)
+            ab = batch.attention_batch("past", self.window)
+            if fast and batch.n_tiles:
+                kind = "prefill_tc" if (hd % 64 == 0 and not batch.has_past) else "prefill"
+            else:
+                kind = "plain"
+            ctx = ops.attention(rows, ab, pages, new_kv=(rows, self.q_width, self.q_width + self.kv_width), kind=kind, **common)
+            if not write_first and pages is not None:
+                ops.rope_norm_cache(rows, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages, seq_end=batch.seq_end)
+        if self.gate is not None:
+            ctx = ops.gate_mul(ctx, rows[:, self.g_col:self.g_col + self.q_width], self.gate)
+        return ops.linear(ctx, self.w_o)
 
     def needs(self):
         return KVRequirement(self.n_kv_heads, self.head_dim, self.window), None
@@ -63,6 +155,8 @@ class Attention:
     delivers_branch = True         # the output projection may deliver the result through a stream's sink
 
     def forward(self, x, batch, cache: RunCache, run: int, sink=None):
+        if self.extended:
+            return self._forward_extended(x, batch, cache)
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         pages = self._pages(batch, cache)
         fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
@@ -158,7 +252,10 @@ def _build_attention(spec: PartSpec, ctx: BuildContext) -> Attention:
     return Attention(hidden_size=p["hidden_size"], n_heads=p["n_heads"], n_kv_heads=p["n_kv_heads"],
                      head_dim=p["head_dim"], score_scale=p["score_scale"], softcap=p.get("softcap"),
                      window=p.get("window"), position=position,
-                     wq=ctx.tensor(t["q"]), wk=ctx.tensor(t["k"]), wv=ctx.tensor(t["v"]), wo=ctx.tensor(t["o"]))
+                     wq=ctx.tensor(t["q"]), wk=ctx.tensor(t["k"]), wv=ctx.tensor(t["v"]), wo=ctx.tensor(t["o"]),
+                     value_dim=p.get("value_dim"), qk_norm_eps=p.get("qk_norm_eps"),
+                     sinks=ctx.tensor(t["sinks"]) if "sinks" in t else None, gate=p.get("gate"),
+                     wg=ctx.tensor(t["g"]) if "g" in t else None)
 
 
 register_part("mixer", "attention", _build_attention, replace=True)

@@ -10,6 +10,9 @@ The model runs its schedule: a list of (layer, whose cache it reads).  A layer n
 twice runs twice, each run with cache storage of its own.  Logits are formed only at the
 rows the step wants (`model.rs:936` forms them at every position).
 
+Post-norm block: x <- norm(alpha x + mixer(x)); x <- norm'(alpha x + ff(x)), for designs that
+norm after the sum; alpha is `LayerSpec.params["alpha"]`.
+
 Interface of a block: `forward(stream: ResidualStream, batch, cache: RunCache, run: int)`;
 it adds its branches to the stream.
 """
@@ -111,6 +114,39 @@ def _build_sandwich(layer: LayerSpec, ctx: BuildContext) -> SandwichBlock:
 register_part("block", "sandwich", _build_sandwich, replace=True)
 
 
+class PostNormBlock:
+    """Norm after the sum: x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ff(x)).  The sublayers read the
+    stream itself (in the activations' dtype), the sum and the norm run in float32 on the stream
+    (`ResidualStream.renorm`); alpha is a parameter of the arrangement.  A layer without a feed-forward ends
+    after the first sublayer."""
+
+    def __init__(self, mixer, feed_forward, norms: Dict[str, object], act_dtype: torch.dtype, alpha: float):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.post_mixer = norms["post_mixer"]
+        self.post_ff = norms["post_feed_forward"] if feed_forward is not None else None
+        self.act_dtype, self.alpha = act_dtype, float(alpha)
+
+    first_norm = None       # it asks the stream for its rows, not for a norm of them
+
+    def forward(self, stream: ResidualStream, batch, cache, run: int):
+        stream.norm_after_block = None
+        a = self.mixer.forward(stream.rows(self.act_dtype), batch, cache, run)
+        stream.renorm(a, self.post_mixer, self.alpha, self.act_dtype)
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(stream.rows(self.act_dtype))
+            stream.renorm(f, self.post_ff, self.alpha, self.act_dtype)
+
+
+def _build_postnorm(layer: LayerSpec, ctx: BuildContext) -> PostNormBlock:
+    mixer = build_part("mixer", layer.mixer, ctx)
+    ff = build_part("feed_forward", layer.feed_forward, ctx) if layer.feed_forward is not None else None
+    norms = {role: build_part("norm", s, ctx) for role, s in layer.norms.items()}
+    return PostNormBlock(mixer, ff, norms, ctx.dtype, layer.params.get("alpha", 1.0))
+
+
+register_part("block", "postnorm", _build_postnorm, replace=True)
+
+
 class Model:
     """A model built from a ModelSpec and loaded tensors.  Nothing here names an architecture."""
 
@@ -124,8 +160,8 @@ class Model:
         for layer in spec.layers:
             self.layers.append(build_block(layer, ctx))
             # parts hold what they need (fused copies or the tensors themselves)
-            for p in (layer.mixer, layer.feed_forward, *layer.norms.values()):
-                for t in (p.tensors.values() if p is not None else ()):
+            for p in (q for top in (layer.mixer, layer.feed_forward, *layer.norms.values()) if top is not None for q in top.walk()):
+                for t in p.tensors.values():
                     if t.name not in keep:
                         weights.pop(t.name, None)
         self.final_norm = build_part("norm", spec.final_norm, ctx)

@@ -79,6 +79,7 @@ class ResidualStream:
         self._pending = None     # (branch: tensor or ops.Branch, post_norm or None)
         self._operand = None     # (bfloat16 [16, hidden] whose first rows are x times a norm's column factors, that norm)
         self._lent = None        # DeferredRows handed out; x is valid once they have been used
+        self._rows = None        # x in the activations' dtype, as `renorm` left it (valid until x changes again)
         self.norm_after_block = None     # a hint the model sets: the norm the stream is asked for first after the current block
 
     # ---- the split form ----
@@ -117,6 +118,7 @@ class ResidualStream:
         nxt = upcoming if (rows is None and upcoming is not None and _fusable(upcoming)) else None
         operand = torch.empty_like(branch.sink.operand) if nxt is not None else None
         d = ops.DeferredRows(branch, out, nxt.fused_params() if nxt is not None else None, operand, rows)
+        self._rows = None
         self.x = out
         self._operand = (operand, nxt) if nxt is not None else None
         self._lent = d
@@ -128,6 +130,7 @@ class ResidualStream:
         `normed` can fuse it.  branch: a tensor, or the `ops.Branch` a sink produced."""
         self._settled()
         self._flush()
+        self._rows = None
         self._pending = (branch, post_norm)
 
     def _flush(self):
@@ -182,3 +185,25 @@ class ResidualStream:
         self._settled()
         self._flush()
         return self.x
+
+    # ---- norm after the sum ----
+    def rows(self, dtype: torch.dtype) -> torch.Tensor:
+        """The stream itself as a part's input: x for float32, else x converted (the copy `renorm` made, if x has not
+        changed since)."""
+        self._settled()
+        self._flush()
+        if dtype is torch.float32:
+            return self.x
+        if self._rows is None or self._rows.dtype is not dtype:
+            self._rows = ops.convert_rows(self.x, dtype)
+        return self._rows
+
+    def renorm(self, branch: torch.Tensor, norm, alpha: float, act_dtype: torch.dtype):
+        """x <- norm(alpha x + branch), sum and norm in float32, one kernel that also leaves x in `act_dtype` for the
+        next part to read.  The norm must be scale-only (`fused_params`)."""
+        self._settled()
+        self._flush()
+        if not _fusable(norm):
+            raise ValueError("renorm: a norm after the sum must offer fused_params() (weight, eps, offset)")
+        self._operand = None
+        self._rows = ops.postnorm_(self.x, branch, norm.fused_params(), alpha, None if act_dtype is torch.float32 else act_dtype)

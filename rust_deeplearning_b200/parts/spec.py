@@ -37,6 +37,13 @@ class PartSpec:
     params: Dict[str, Any] = field(default_factory=dict)
     tensors: Dict[str, TensorSpec] = field(default_factory=dict)
 
+    def walk(self):
+        """This part and the parts named in its parameters (a position encoding, the two halves of a pair), depth first."""
+        yield self
+        for v in self.params.values():
+            if isinstance(v, PartSpec):
+                yield from v.walk()
+
 
 @dataclass(frozen=True)
 class LayerSpec:
@@ -45,6 +52,7 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward: Optional[PartSpec]      # None: the layer has a mixer only
     norms: Dict[str, PartSpec]
+    params: Dict[str, Any] = field(default_factory=dict)     # constants of the arrangement itself (a post-norm block's alpha)
 
 
 @dataclass(frozen=True)
@@ -76,9 +84,9 @@ class ModelSpec:
     def part_specs(self):
         yield self.embedding
         for layer in self.layers:
-            yield layer.mixer
+            yield from layer.mixer.walk()
             if layer.feed_forward is not None:
-                yield layer.feed_forward
+                yield from layer.feed_forward.walk()
             for n in layer.norms.values():
                 yield n
         yield self.final_norm
