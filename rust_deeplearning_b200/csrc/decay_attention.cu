@@ -157,9 +157,278 @@ extern "C" int rdl_decay_attention_scan(const DecayAttentionArgs* a, void* strea
     return a->dtype == RDL_BF16 ? launch_scan<__nv_bfloat16>(a, (cudaStream_t)stream) : launch_scan<float>(a, (cudaStream_t)stream);
 }
 
+// ---- the chunked form, for many tokens in bfloat16 ----
+//
+// With chunks of C = 64 tokens, S the state before a chunk's first token, L the chunk's tokens and i, j places inside it:
+//   o_i   = sum_{j <= i} d^(i-j) (q_i . k_j) v_j  +  d^(i+1) S^T q_i
+//   S'    = d^L S + sum_j d^(L-1-j) k_j v_j^T.
+// A block walks one sequence's chunks for one head and 64 columns of the state (a column of S decides the same
+// column of o alone).  Per chunk its four warps
+//   1. bring q, k, v of the chunk into shared memory as they enter the recurrence (rotation, SiLU and k's constant in
+//      float, rounded to bfloat16 once), and v times d^(L-1-j) for the state;
+//   2. form P = (Q K^T) * d^(i-j) on tensor cores (16 rows a warp), the powers of d applied to the float sums;
+//   3. O = P V, and O += d^(i+1) (Q S): S is float and enters the product as two bfloat16 terms (its rounding and the
+//      remainder's), so the state's 24 bits are not cut to 8 on the way;
+//   4. S' = d^L S + K^T V_d with S in the registers of the warps as the product's accumulator, float throughout.
+// The powers d^n are exp2(n log2 d) in float (d^0 = 1 also for d = 0).
+#include <mma.h>
+
+#define DC_CHUNK 64
+#define DC_COLS 64
+#define DC_THREADS 128
+#define DC_PAD 8            // bfloat16 values between rows in shared memory: ldmatrix reads eight rows without bank conflicts
+
+__device__ __forceinline__ uint32_t dc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void dc_ldm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dc_ldm4t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dc_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t dc_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(DC_THREADS) decay_chunk_kernel(DecayAttentionArgs a) {
+    extern __shared__ __align__(16) unsigned char dc_raw[];
+    const int dim = a.dim, vdim = a.vdim;
+    const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DC_COLS;
+    const int nv = min(DC_COLS, vdim - c0);              // columns of this block (a multiple of 16)
+    const int qs = dim + DC_PAD, vs = DC_COLS + DC_PAD;   // row strides in shared memory, in values
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(dc_raw);     // [64][qs]
+    __nv_bfloat16* Ks = Qs + DC_CHUNK * qs;                             // [64][qs]
+    __nv_bfloat16* Vs = Ks + DC_CHUNK * qs;                             // [64][vs]
+    __nv_bfloat16* Vd = Vs + DC_CHUNK * vs;                             // [64][vs]  v times d^(L-1-j)
+    __nv_bfloat16* Sh = Vd + DC_CHUNK * vs;                             // [dim][vs] the state, rounded
+    __nv_bfloat16* Sl = Sh + dim * vs;                                  // [dim][vs] what the rounding left
+    float* pw = reinterpret_cast<float*>(Sl + dim * vs);               // [65] d^n
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int row0 = a.seq_start[seq], n = a.seq_start[seq + 1] - row0;
+    if (n <= 0) return;
+    if (a.tok_pos[row0] < 0) return;         // a padding sequence of a fixed-size batch
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+    const float decay = a.decay[h];
+    const float lg = decay > 0.f ? log2f(decay) : 0.f;
+    for (int d = tid; d <= DC_CHUNK; d += DC_THREADS) pw[d] = d == 0 ? 1.f : (decay > 0.f ? exp2f((float)d * lg) : 0.f);
+    const int ksteps = dim >> 4, n_mt = dim >> 4, nt_count = nv >> 3;
+    float* S = a.state + (((long long)a.slots[seq] * a.n_heads + h) * dim) * vdim + c0;
+    // the state's rows 16 (warp + 4 mi) .. + 15 are this warp's, as accumulators: (row g, g + 8; columns 8 nt + 2 tq, + 1)
+    float sacc[2][8][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+        const int m0 = (warp + 4 * mi) * 16;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = m0 + g + 8 * (e >> 1), c = nt * 8 + 2 * tq + (e & 1);
+                sacc[mi][nt][e] = (warp + 4 * mi < n_mt && nt < nt_count) ? S[(long long)r * vdim + c] : 0.f;
+            }
+        }
+    }
+    auto put_state = [&]() {       // the state as two bfloat16 terms, for the next chunk's Q S
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+            if (warp + 4 * mi >= n_mt) continue;
+            const int m0 = (warp + 4 * mi) * 16;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                if (nt >= nt_count) continue;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float x = sacc[mi][nt][2 * hh], y = sacc[mi][nt][2 * hh + 1];
+                    const __nv_bfloat162 hi = __floats2bfloat162_rn(x, y);
+                    const float2 hf = __bfloat1622float2(hi);
+                    const int off = (m0 + g + 8 * hh) * vs + nt * 8 + 2 * tq;
+                    *reinterpret_cast<__nv_bfloat162*>(Sh + off) = hi;
+                    *reinterpret_cast<__nv_bfloat162*>(Sl + off) = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+                }
+            }
+        }
+    };
+    put_state();
+    const __nv_bfloat16* rows = (const __nv_bfloat16*)a.rows;
+    const int half = a.rot_n >> 1;
+    const int i_hi = warp * 16 + g + 8;     // this thread's rows of a chunk: i_hi - 8 and i_hi
+
+    for (int t0 = 0; t0 < n; t0 += DC_CHUNK) {
+        const int L = min(DC_CHUNK, n - t0);
+        // ---- 1. q, k, v as they enter the recurrence ----
+        for (int idx = tid; idx < DC_CHUNK * dim; idx += DC_THREADS) {
+            const int j = idx / dim, i = idx - j * dim;
+            float qv = 0.f, kv = 0.f;
+            if (j < L) {
+                const __nv_bfloat16* row = rows + (long long)(row0 + t0 + j) * a.row_stride;
+                const __nv_bfloat16* qr = row + a.q_col + h * dim;
+                const __nv_bfloat16* kr = row + a.k_col + h * dim;
+                if (i < 2 * half) {
+                    const int pos = a.tok_pos[row0 + t0 + j];
+                    const int f = i < half ? i : i - half;
+                    const float cs = a.cos_t[(long long)pos * half + f], sn = a.sin_t[(long long)pos * half + f];
+                    const float q1 = __bfloat162float(qr[f]), q2 = __bfloat162float(qr[f + half]);
+                    const float k1 = __bfloat162float(kr[f]), k2 = __bfloat162float(kr[f + half]);
+                    qv = i < half ? q1 * cs - q2 * sn : q2 * cs + q1 * sn;
+                    kv = i < half ? k1 * cs - k2 * sn : k2 * cs + k1 * sn;
+                } else {
+                    qv = __bfloat162float(qr[i]);
+                    kv = __bfloat162float(kr[i]);
+                }
+                if (a.silu) { qv = silu_f(qv); kv = silu_f(kv); }
+                kv *= a.k_scale;
+            }
+            Qs[j * qs + i] = __float2bfloat16_rn(qv);
+            Ks[j * qs + i] = __float2bfloat16_rn(kv);
+        }
+        for (int idx = tid; idx < DC_CHUNK * nv; idx += DC_THREADS) {
+            const int j = idx / nv, c = idx - j * nv;
+            float v = 0.f;
+            if (j < L) {
+                v = __bfloat162float(rows[(long long)(row0 + t0 + j) * a.row_stride + a.v_col + h * vdim + c0 + c]);
+                if (a.silu) v = silu_f(v);
+            }
+            Vs[j * vs + c] = __float2bfloat16_rn(v);
+            Vd[j * vs + c] = __float2bfloat16_rn(j < L ? v * pw[L - 1 - j] : 0.f);
+        }
+        __syncthreads();
+
+        // ---- 2. P = (Q K^T) d^(i-j), rows 16 warp .. + 15 ----
+        uint32_t qf[8][4];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+            if (kk < ksteps) dc_ldm4(qf[kk], dc_smem(Qs + (warp * 16 + (lane & 15)) * qs + kk * 16 + 8 * (lane >> 4)));
+        float p[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) p[nt][0] = p[nt][1] = p[nt][2] = p[nt][3] = 0.f;
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            if (np * 16 > warp * 16 + 15) continue;          // keys after this warp's last row
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                if (kk >= ksteps) continue;
+                uint32_t bf[4];
+                dc_ldm4(bf, dc_smem(Ks + (np * 16 + ((lane >> 4) << 3) + (lane & 7)) * qs + kk * 16 + (((lane >> 3) & 1) << 3)));
+                dc_mma(p[2 * np], qf[kk], bf[0], bf[1]);
+                dc_mma(p[2 * np + 1], qf[kk], bf[2], bf[3]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = i_hi - 8 + 8 * (e >> 1), j = nt * 8 + 2 * tq + (e & 1);
+                p[nt][e] = j <= i ? p[nt][e] * pw[i - j] : 0.f;
+            }
+        }
+        // ---- 3. O = P V + d^(i+1) Q S ----
+        float o[8][4], o2[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; o2[nt][0] = o2[nt][1] = o2[nt][2] = o2[nt][3] = 0.f; }
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+            if (kb * 16 > warp * 16 + 15) continue;
+            uint32_t pa[4] = {dc_pack(p[2 * kb][0], p[2 * kb][1]), dc_pack(p[2 * kb][2], p[2 * kb][3]),
+                              dc_pack(p[2 * kb + 1][0], p[2 * kb + 1][1]), dc_pack(p[2 * kb + 1][2], p[2 * kb + 1][3])};
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                if (2 * nb >= nt_count) continue;
+                uint32_t bf[4];
+                dc_ldm4t(bf, dc_smem(Vs + (kb * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * vs + nb * 16 + ((lane >> 4) << 3)));
+                dc_mma(o[2 * nb], pa, bf[0], bf[1]);
+                dc_mma(o[2 * nb + 1], pa, bf[2], bf[3]);
+            }
+        }
+        if (t0 > 0 || true) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                if (kk >= ksteps) continue;
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    if (2 * nb >= nt_count) continue;
+                    const int off = (kk * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * vs + nb * 16 + ((lane >> 4) << 3);
+                    uint32_t bh[4], bl[4];
+                    dc_ldm4t(bh, dc_smem(Sh + off));
+                    dc_ldm4t(bl, dc_smem(Sl + off));
+                    dc_mma(o2[2 * nb], qf[kk], bh[0], bh[1]);
+                    dc_mma(o2[2 * nb + 1], qf[kk], bh[2], bh[3]);
+                    dc_mma(o2[2 * nb], qf[kk], bl[0], bl[1]);
+                    dc_mma(o2[2 * nb + 1], qf[kk], bl[2], bl[3]);
+                }
+            }
+        }
+        {
+            const float w_lo = pw[i_hi - 8 + 1], w_hi = pw[i_hi + 1];
+            float* out_lo = a.out + (long long)(row0 + t0 + i_hi - 8) * a.n_heads * vdim + (long long)h * vdim + c0;
+            float* out_hi = out_lo + 8LL * a.n_heads * vdim;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                if (nt >= nt_count) continue;
+                const int c = nt * 8 + 2 * tq;
+                if (i_hi - 8 < L) *reinterpret_cast<float2*>(out_lo + c) = make_float2(fmaf(w_lo, o2[nt][0], o[nt][0]), fmaf(w_lo, o2[nt][1], o[nt][1]));
+                if (i_hi < L) *reinterpret_cast<float2*>(out_hi + c) = make_float2(fmaf(w_hi, o2[nt][2], o[nt][2]), fmaf(w_hi, o2[nt][3], o[nt][3]));
+            }
+        }
+        // ---- 4. S' = d^L S + K^T V_d ----
+        const float dl = pw[L];
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+            if (warp + 4 * mi >= n_mt) continue;
+            const int m0 = (warp + 4 * mi) * 16;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) { sacc[mi][nt][0] *= dl; sacc[mi][nt][1] *= dl; sacc[mi][nt][2] *= dl; sacc[mi][nt][3] *= dl; }
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                uint32_t ka[4];
+                dc_ldm4t(ka, dc_smem(Ks + (kb * 16 + ((lane >> 4) << 3) + (lane & 7)) * qs + m0 + (((lane >> 3) & 1) << 3)));
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    if (2 * nb >= nt_count) continue;
+                    uint32_t bf[4];
+                    dc_ldm4t(bf, dc_smem(Vd + (kb * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * vs + nb * 16 + ((lane >> 4) << 3)));
+                    dc_mma(sacc[mi][2 * nb], ka, bf[0], bf[1]);
+                    dc_mma(sacc[mi][2 * nb + 1], ka, bf[2], bf[3]);
+                }
+            }
+        }
+        __syncthreads();            // every warp is through with this chunk's rows and with the old state's terms
+        if (t0 + DC_CHUNK < n) put_state();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+        if (warp + 4 * mi >= n_mt) continue;
+        const int m0 = (warp + 4 * mi) * 16;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            if (nt >= nt_count) continue;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                *reinterpret_cast<float2*>(S + (long long)(m0 + g + 8 * hh) * vdim + nt * 8 + 2 * tq) =
+                    make_float2(sacc[mi][nt][2 * hh], sacc[mi][nt][2 * hh + 1]);
+        }
+    }
+}
+
 extern "C" int rdl_decay_attention_chunked(const DecayAttentionArgs* a, void* stream) {
-    (void)stream;
     if (int e = check_decay_args(a, "decay_attention_chunked")) return e;
-    RDL_REQUIRE(false, "decay_attention_chunked: not available");
+    RDL_REQUIRE(a->dtype == RDL_BF16, "decay_attention_chunked: bfloat16 rows only");
+    RDL_REQUIRE(a->dim % 16 == 0 && a->dim <= 128 && a->vdim % 16 == 0, "decay_attention_chunked: dim %d and vdim %d must be multiples of 16, dim at most 128",
+                a->dim, a->vdim);
+    RDL_REQUIRE(((uintptr_t)a->out & 7) == 0 && ((uintptr_t)a->state & 7) == 0, "decay_attention_chunked: output and state must be 8-byte aligned");
+    if (a->n_tokens == 0 || a->n_seqs == 0) return 0;
+    const int qs = a->dim + DC_PAD, vs = DC_COLS + DC_PAD;
+    const size_t smem = (size_t)(2 * DC_CHUNK * qs + 2 * DC_CHUNK * vs + 2 * a->dim * vs) * 2 + (DC_CHUNK + 1) * sizeof(float) + 16;
+    static bool opted = false;
+    if (!opted) {
+        RDL_CUDA(cudaFuncSetAttribute(decay_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024), "decay_attention_chunked");
+        opted = true;
+    }
+    const dim3 grid(a->n_seqs, a->n_heads, (a->vdim + DC_COLS - 1) / DC_COLS);
+    RDL_CHECK_EX(rdl_launch(decay_chunk_kernel, grid, dim3(DC_THREADS), smem, (cudaStream_t)stream, *a), "decay_attention_chunked");
     return 0;
 }

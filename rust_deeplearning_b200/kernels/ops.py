@@ -1063,7 +1063,7 @@ def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param:
 # ------------------------------------------------------------------------------------------
 
 DECAY_CHUNKED_MIN_TOKENS = 64    # from this many rows on a bfloat16 step takes the chunked tensor-core kernel
-DECAY_CHUNKED = os.environ.get("RDL_DECAY_ATTENTION", "scan") != "scan"     # "scan": token by token everywhere, for comparison
+DECAY_CHUNKED = os.environ.get("RDL_DECAY_ATTENTION", "chunked") != "scan"     # "scan": token by token everywhere, for comparison
 
 
 def decay_attention_chunked_ok(dtype, dim: int, vdim: int) -> bool:
