@@ -246,16 +246,30 @@ def ligirax_shape(width, heads, dim, rot_dim, vdim, kv_rank, window, experts, id
             "max_positions": CONTEXT, "layers": out}
 
 
-def gemma_like(width, heads, head_dim, intermediate, window, layers, vocab):
+def gemma_like(width, heads, head_dim, intermediate, window, layers, vocab, kv_heads=None):
     """The Gemma 2 configuration with the same width, head count and window, whose feed-forward is as wide as the
-    experts a Ligirax token uses."""
-    return dict(GEMMA2_2B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=heads,
-                head_dim=head_dim, intermediate_size=intermediate, vocab_size=vocab, sliding_window=window,
-                query_pre_attn_scalar=head_dim, max_position_embeddings=CONTEXT)
+    experts a Ligirax token uses (as wide as Dokulorn's dense feed-forward)."""
+    return dict(GEMMA2_2B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=kv_heads or heads, head_dim=head_dim, intermediate_size=intermediate, vocab_size=vocab,
+                sliding_window=window, query_pre_attn_scalar=head_dim, max_position_embeddings=CONTEXT)
+
+
+def dokulorn_shape(width, heads, kv_heads, dim, ff, layers, vocab):
+    """A Dokulorn configuration of `layers` layers, each with a dense feed-forward: retention layers, and every fourth
+    layer a pair (softmax attention with grouped key/value heads beside lightning attention)."""
+    decay = [1.0 - 2.0 ** (-5 - 5 * h / max(heads - 1, 1)) for h in range(heads)]
+    ret = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay, "rot": {"base": 1e6, "dims": dim}}
+    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "rot": {"base": 1e4, "dims": dim // 2},
+                    "scale": 1.0, "softcap": 20.0},
+           "right": {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}}
+    out = [{"type": "parallel" if i % 4 == 3 else "retention", "mixer": par if i % 4 == 3 else ret, "mlp": {"kind": "dense", "ff": ff}}
+           for i in range(layers)]
+    return {"architecture": "Dokulorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "embedding": {"scale": 10.0}, "max_positions": CONTEXT, "layers": out}
 
 
 DESIGN_SIZES = {
-    # name: (Ligirax arguments, the Gemma 2 arguments of equal width / heads / active feed-forward width)
+    # name: (the design's arguments, the Gemma 2 arguments of equal width / heads / active feed-forward width)
     "w1024": (dict(width=1024, heads=8, dim=64, rot_dim=64, vdim=128, kv_rank=192, window=1024, experts=16, identity=2, top=2, ff=1024,
                    layers=4, vocab=32000, shared_from=1),
               dict(width=1024, heads=8, head_dim=128, intermediate=2048, window=1024, layers=4, vocab=32000)),
@@ -263,6 +277,16 @@ DESIGN_SIZES = {
                    layers=4, vocab=32000),
               dict(width=2048, heads=16, head_dim=128, intermediate=8448, window=4096, layers=4, vocab=32000)),
 }
+DOKULORN_SIZES = {
+    # four layers each: three retention layers and a pair, all with a dense feed-forward; Gemma 2 with the same width,
+    # heads, head size and feed-forward width (its windows as long as the context: all keys are read)
+    "w1024": (dict(width=1024, heads=8, kv_heads=4, dim=128, ff=4096, layers=4, vocab=32000),
+              dict(width=1024, heads=8, kv_heads=4, head_dim=128, intermediate=4096, window=CONTEXT, layers=4, vocab=32000)),
+    "w2048": (dict(width=2048, heads=16, kv_heads=8, dim=128, ff=8192, layers=4, vocab=32000),
+              dict(width=2048, heads=16, kv_heads=8, head_dim=128, intermediate=8192, window=CONTEXT, layers=4, vocab=32000)),
+}
+DESIGNS = {"ligirax": (ligirax_shape, DESIGN_SIZES, "ligirax beside gemma2 at equal width, heads and active feed-forward width"),
+           "dokulorn": (dokulorn_shape, DOKULORN_SIZES, "dokulorn beside gemma2 at equal width, heads, head size and feed-forward width")}
 
 
 def design_point(cfg, vocab, torch, rng, steps, warmup, prompt_len, batches, long_prompt=CONTEXT):
@@ -327,14 +351,15 @@ def design_comparison(args):
     clocks = ClockSampler()
     clocks.start()
     sizes = {}
-    for name, (lig, gem) in DESIGN_SIZES.items():
+    shape_of, table, title = DESIGNS[args.design]
+    for name, (lig, gem) in table.items():
         if args.size and name != args.size:
             continue
         sizes[name] = {
-            "ligirax": design_point(ligirax_shape(**lig), lig["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
+            args.design: design_point(shape_of(**lig), lig["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
             "gemma2": design_point(gemma_like(**gem), gem["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
-            "shapes": {"ligirax": lig, "gemma2": gem}}
-    print(json.dumps({"design": "ligirax beside gemma2 at equal width, heads and active feed-forward width", "dtype": "bf16",
+            "shapes": {args.design: lig, "gemma2": gem}}
+    print(json.dumps({"design": title, "dtype": "bf16",
                       "data": "synthetic: random weights, seeded uniform-random token ids", "prompt_len": PROMPT,
                       "sizes": sizes, "clocks": clocks.stop(), "peaks": peaks()}))
     return 0
@@ -352,7 +377,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="batch of the --only decode case")
     ap.add_argument("--context", type=int, default=PROMPT, help="prompt length of the --only decode case")
     ap.add_argument("--no-large", action="store_true", help="leave out the 9B and 27B shapes and the long contexts")
-    ap.add_argument("--design", choices=["ligirax"], default=None,
+    ap.add_argument("--design", choices=["ligirax", "dokulorn"], default=None,
                     help="instead of the default workload: prefill and decode of this design beside Gemma 2 at equal layer sizes")
     ap.add_argument("--size", default=None, help="with --design: one of the sizes only")
     args = ap.parse_args()
