@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 14
+#define RDL_ABI_VERSION 15
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -154,8 +154,10 @@ typedef struct {
 } DecayAttentionArgs;
 // token by token, float throughout: the 32-bit path, single-token steps, and the reference of the chunked kernel
 int rdl_decay_attention_scan(const DecayAttentionArgs* a, void* stream);
-// bfloat16 rows, many tokens: chunks of 64 tokens on tensor cores, the state in float between chunks
-int rdl_decay_attention_chunked(const DecayAttentionArgs* a, void* stream);
+// bfloat16 rows, many tokens: chunks of 64 tokens on tensor cores, the state in float between chunks.  work: a float
+// buffer of rdl_decay_attention_chunks(n_tokens, n_seqs) * n_heads * dim * vdim values (a state per chunk and head).
+int rdl_decay_attention_chunks(int n_tokens, int n_seqs);
+int rdl_decay_attention_chunked(const DecayAttentionArgs* a, void* work, long long work_bytes, void* stream);
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float, plain FMA in a fixed order of k
 int rdl_gemm_f32(void* out, const void* x, const void* w, int m, int n, int k, void* stream);

@@ -313,7 +313,11 @@ extern "C" int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, 
                     (k_cache && v_cache && tables && seq_end && page_size > 0 && ring_pages > 0 && ring_pages <= table_width),
                 "rope_norm_cache: cache write needs storage, page tables and lengths");
     if (n_tokens == 0) return 0;
-    const int warps = 4;
+    // a warp per head while a block's shared memory and thread count allow it: a head is three dependent steps
+    // (load and rotate, sum, scale and store), so heads one after another in a warp are trips to memory one after another
+    int warps = n_heads + 2 * n_kv_heads;
+    if (warps > 16) warps = 16;
+    while (warps > 1 && (size_t)warps * head_dim * sizeof(float) > 40 * 1024) warps /= 2;
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;

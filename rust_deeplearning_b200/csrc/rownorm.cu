@@ -5,6 +5,178 @@
 #include "common.cuh"
 #include "launch.cuh"
 
+__device__ __forceinline__ float gate_value(float g, int act) {
+    const float s = 1.0f / (1.0f + expf(-g));
+    return act == RDL_GATE_SILU ? g * s : s;
+}
+
+// Four consecutive values at a time, and a row (or group) held in registers between its two passes: every load of a
+// thread is asked for before the first is used, so a row costs one trip to memory however wide it is.  Used when
+// the width is a multiple of 4 and a thread's share fits RN_MAX_IT groups of four; the plain loops further down serve the rest.
+#define RN_MAX_IT 8
+__device__ __forceinline__ void rn_load4(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void rn_load4(const __nv_bfloat16* p, float (&f)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void rn_load4(const void* p, long long i, int dtype, float (&f)[4]) {
+    if (dtype == RDL_BF16) rn_load4((const __nv_bfloat16*)p + i, f); else rn_load4((const float*)p + i, f);
+}
+__device__ __forceinline__ void rn_store4(float* p, const float (&f)[4]) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+__device__ __forceinline__ void rn_store4(__nv_bfloat16* p, const float (&f)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&a); raw.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+// threads of a block whose row is `width` wide: a multiple of 32 that depends on the width alone
+static inline int vec_threads(int width) {
+    const int groups = width / 4;
+    int t = (groups + RN_MAX_IT - 1) / RN_MAX_IT;      // the fewest that keep a thread's share within RN_MAX_IT
+    if (t < (groups + 1) / 2) t = (groups + 1) / 2;    // but two groups a thread at most while a block holds them
+    t = (t + 31) / 32 * 32;
+    return t > 256 ? 256 : (t < 32 ? 32 : t);
+}
+static inline bool vec_ok(int width, int threads) { return width % 4 == 0 && (width / 4 + threads - 1) / threads <= RN_MAX_IT; }
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+template <typename TB, typename TY>
+__global__ void __launch_bounds__(256) postnorm_vec_kernel(float* __restrict__ res, const TB* __restrict__ branch, float alpha,
+                                                           const void* __restrict__ w, int w_dtype, float eps, float off,
+                                                           TY* __restrict__ y, int width) {
+    __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    float* r = res + (long long)blockIdx.x * width;
+    const TB* b = branch + (long long)blockIdx.x * width;
+    float h[RN_MAX_IT][4], bv[RN_MAX_IT][4];
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) { rn_load4(r + e, h[it]); rn_load4(b + e, bv[it]); }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { h[it][k] = fmaf(alpha, h[it][k], bv[it][k]); ss = fmaf(h[it][k], h[it][k], ss); }
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+            float wv[4], v[4];
+            rn_load4(w, e, w_dtype, wv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = h[it][k] * inv * (wv[k] + off);
+            rn_store4(r + e, v);
+            if (y) rn_store4(y + (long long)blockIdx.x * width + e, v);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) norm_pair_vec_kernel(float* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
+                                                            const void* __restrict__ wa, const void* __restrict__ wb, int w_dtype,
+                                                            float eps, float c, int width) {
+    __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const T* ra = a + (long long)blockIdx.x * width;
+    const T* rb = b + (long long)blockIdx.x * width;
+    float x[RN_MAX_IT][4], z[RN_MAX_IT][4];
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) { rn_load4(ra + e, x[it]); rn_load4(rb + e, z[it]); }
+    }
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { sa = fmaf(x[it][k], x[it][k], sa); sb = fmaf(z[it][k], z[it][k], sb); }
+        }
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ia = 1.0f / sqrtf(sa / (float)width + eps), ib = 1.0f / sqrtf(sb / (float)width + eps);
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+            float va[4], vb[4], v[4];
+            rn_load4(wa, e, w_dtype, va);
+            rn_load4(wb, e, w_dtype, vb);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = c * (x[it][k] * ia * va[k] + z[it][k] * ib * vb[k]);
+            rn_store4(out + (long long)blockIdx.x * width + e, v);
+        }
+    }
+}
+
+// a warp per group (groups of up to 1,024 values), or a block per group (WARP false)
+template <typename TO, bool WARP>
+__global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, long long n_items, int groups,
+                                                                  int group, const void* __restrict__ w, int w_dtype, float eps,
+                                                                  const void* __restrict__ g, long long g_stride, int g_dtype, int act) {
+    __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const long long item = WARP ? (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+    if (WARP && item >= n_items) return;
+    const int lane = WARP ? (threadIdx.x & 31) : threadIdx.x, stride = WARP ? 32 : blockDim.x;
+    const long long t = item / groups;
+    const int gi = (int)(item - t * groups), col0 = gi * group;
+    const long long base = item * group;
+    float v[RN_MAX_IT][4], gv[RN_MAX_IT][4];
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (lane + it * stride) * 4;
+        if (e < group) {
+            rn_load4(x + base + e, v[it]);
+            if (g) rn_load4(g, t * g_stride + col0 + e, g_dtype, gv[it]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (lane + it * stride) * 4;
+        if (e < group) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ss = fmaf(v[it][k], v[it][k], ss);
+        }
+    }
+    ss = WARP ? warp_sum(ss) : block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)group + eps);
+#pragma unroll
+    for (int it = 0; it < RN_MAX_IT; ++it) {
+        const int e = (lane + it * stride) * 4;
+        if (e < group) {
+            float o[4], wv[4];
+            if (w) rn_load4(w, col0 + e, w_dtype, wv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o[k] = v[it][k] * inv;
+                if (w) o[k] *= wv[k];
+                if (g) o[k] *= gate_value(gv[it][k], act);
+            }
+            rn_store4(out + base + e, o);
+        }
+    }
+}
+
 static inline int row_threads(int width) { return width <= 256 ? 64 : (width <= 2048 ? 128 : 256); }
 
 // res <- norm(alpha * res + branch); y (optional) the same rows in another type
@@ -37,8 +209,29 @@ extern "C" int rdl_postnorm(float* res, const void* branch, int branch_dtype, fl
     RDL_REQUIRE(res && branch && w && n_rows >= 0 && width > 0, "postnorm: missing rows or weight");
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const dim3 grid(n_rows), block(row_threads(width));
     cudaError_t e;
+    const int vt = vec_threads(width);
+    if (vec_ok(width, vt) && aligned16(res) && aligned16(branch) && aligned16(w) && aligned16(y)) {
+        const dim3 grid(n_rows), block(vt);
+        if (branch_dtype == RDL_BF16) {
+            if (y_dtype == RDL_BF16)
+                e = rdl_launch(postnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, st, res, (const __nv_bfloat16*)branch, alpha,
+                               w, w_dtype, eps, off, (__nv_bfloat16*)y, width);
+            else
+                e = rdl_launch(postnorm_vec_kernel<__nv_bfloat16, float>, grid, block, 0, st, res, (const __nv_bfloat16*)branch, alpha, w,
+                               w_dtype, eps, off, (float*)y, width);
+        } else {
+            if (y_dtype == RDL_BF16)
+                e = rdl_launch(postnorm_vec_kernel<float, __nv_bfloat16>, grid, block, 0, st, res, (const float*)branch, alpha, w, w_dtype,
+                               eps, off, (__nv_bfloat16*)y, width);
+            else
+                e = rdl_launch(postnorm_vec_kernel<float, float>, grid, block, 0, st, res, (const float*)branch, alpha, w, w_dtype, eps, off,
+                               (float*)y, width);
+        }
+        RDL_CHECK_EX(e, "postnorm");
+        return 0;
+    }
+    const dim3 grid(n_rows), block(row_threads(width));
     if (branch_dtype == RDL_BF16) {
         if (y_dtype == RDL_BF16)
             e = rdl_launch(postnorm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, st, res, (const __nv_bfloat16*)branch, alpha, w,
@@ -90,6 +283,17 @@ extern "C" int rdl_norm_pair(float* out, const void* a, const void* b, int dtype
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
+    const int vt = vec_threads(width);
+    if (vec_ok(width, vt) && aligned16(out) && aligned16(a) && aligned16(b) && aligned16(wa) && aligned16(wb)) {
+        if (dtype == RDL_BF16)
+            e = rdl_launch(norm_pair_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vt), 0, st, out, (const __nv_bfloat16*)a,
+                           (const __nv_bfloat16*)b, wa, wb, w_dtype, eps, c, width);
+        else
+            e = rdl_launch(norm_pair_vec_kernel<float>, dim3(n_rows), dim3(vt), 0, st, out, (const float*)a, (const float*)b, wa, wb,
+                           w_dtype, eps, c, width);
+        RDL_CHECK_EX(e, "norm_pair");
+        return 0;
+    }
     if (dtype == RDL_BF16)
         e = rdl_launch(norm_pair_kernel<__nv_bfloat16>, dim3(n_rows), dim3(row_threads(width)), 0, st, out, (const __nv_bfloat16*)a,
                        (const __nv_bfloat16*)b, wa, wb, w_dtype, eps, c, width);
@@ -100,10 +304,6 @@ extern "C" int rdl_norm_pair(float* out, const void* a, const void* b, int dtype
     return 0;
 }
 
-__device__ __forceinline__ float gate_value(float g, int act) {
-    const float s = 1.0f / (1.0f + expf(-g));
-    return act == RDL_GATE_SILU ? g * s : s;
-}
 
 template <typename T>
 __global__ void gate_mul_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
@@ -172,8 +372,26 @@ extern "C" int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int
     RDL_REQUIRE(!g || g_stride >= (long long)groups * group, "group_norm_gate: the gate's rows are narrower than the groups");
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const dim3 grid(n_rows, groups), block(group <= 64 ? 32 : row_threads(group));
     cudaError_t e;
+    const long long n_items = (long long)n_rows * groups;
+    const bool all16 = aligned16(out) && aligned16(x) && aligned16(w) && aligned16(g) && (!g || g_stride % 8 == 0);
+    if (all16 && group % 8 == 0 && n_items < (1LL << 31)) {
+        const bool warp = group <= 4 * 32 * RN_MAX_IT;
+        const int vt = vec_threads(group);
+        if (warp || vec_ok(group, vt)) {
+            const dim3 grid(warp ? (unsigned)((n_items + 7) / 8) : (unsigned)n_items), block(warp ? 256 : vt);
+            if (out_dtype == RDL_BF16) {
+                if (warp) e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, true>, grid, block, 0, st, (__nv_bfloat16*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
+                else e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, false>, grid, block, 0, st, (__nv_bfloat16*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
+            } else {
+                if (warp) e = rdl_launch(group_norm_gate_vec_kernel<float, true>, grid, block, 0, st, (float*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
+                else e = rdl_launch(group_norm_gate_vec_kernel<float, false>, grid, block, 0, st, (float*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
+            }
+            RDL_CHECK_EX(e, "group_norm_gate");
+            return 0;
+        }
+    }
+    const dim3 grid(n_rows, groups), block(group <= 64 ? 32 : row_threads(group));
     if (out_dtype == RDL_BF16)
         e = rdl_launch(group_norm_gate_kernel<__nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)out, x, groups, group, w, w_dtype, eps, g,
                        g_stride, g_dtype, gate_act);

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 14
+ABI_VERSION = 15
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -276,7 +276,8 @@ _SIGNATURES = {
     "rdl_gate_mul": [_P, _LL, _P, _LL, _P, _LL, _I, _I, _I, _I, _P],
     "rdl_group_norm_gate": [_P, _I, _P, _I, _I, _I, _P, _I, _F, _P, _LL, _I, _I, _P],
     "rdl_decay_attention_scan": [ctypes.POINTER(DecayAttentionArgs), _P],
-    "rdl_decay_attention_chunked": [ctypes.POINTER(DecayAttentionArgs), _P],
+    "rdl_decay_attention_chunked": [ctypes.POINTER(DecayAttentionArgs), _P, _LL, _P],
+    "rdl_decay_attention_chunks": [_I, _I],
     "rdl_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     "rdl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "rdl_gemm_skinny_norm": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, ctypes.POINTER(DeferredNormArgs), _P, _P],

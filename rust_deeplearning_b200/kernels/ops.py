@@ -1063,6 +1063,7 @@ def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param:
 # ------------------------------------------------------------------------------------------
 
 DECAY_CHUNKED_MIN_TOKENS = 64    # from this many rows on a bfloat16 step takes the chunked tensor-core kernel
+DECAY_CHUNKED_MIN_PER_SEQUENCE = 8    # ... and this many rows a sequence on average
 DECAY_CHUNKED = os.environ.get("RDL_DECAY_ATTENTION", "chunked") != "scan"     # "scan": token by token everywhere, for comparison
 
 
@@ -1107,13 +1108,17 @@ def decay_attention(rows: torch.Tensor, *, q_col: int, k_col: int, v_col: int, n
     a.decay, a.tok_pos, a.seq_start, a.slots = decay.data_ptr(), tok_pos.data_ptr(), seq_start.data_ptr(), slots.data_ptr()
     a.state, a.out = state.data_ptr(), out.data_ptr()
     if kind == "auto":
-        kind = "chunked" if (DECAY_CHUNKED and T >= DECAY_CHUNKED_MIN_TOKENS and decay_attention_chunked_ok(rows.dtype, dim, vdim)) else "scan"
+        # chunks pay when sequences bring many tokens each; a step of single tokens (any batch) reads and writes each state once
+        many = T >= DECAY_CHUNKED_MIN_TOKENS and T >= DECAY_CHUNKED_MIN_PER_SEQUENCE * n_seqs
+        kind = "chunked" if (DECAY_CHUNKED and many and decay_attention_chunked_ok(rows.dtype, dim, vdim)) else "scan"
     lib = library.load()
     if kind == "scan":
         library.check(lib.rdl_decay_attention_scan(ctypes.byref(a), _stream(rows)))
     elif kind == "chunked":
         _need(decay_attention_chunked_ok(rows.dtype, dim, vdim), "decay_attention: the chunked kernel takes bfloat16 heads of 16..128 values in steps of 16")
-        library.check(lib.rdl_decay_attention_chunked(ctypes.byref(a), _stream(rows)))
+        chunks = lib.rdl_decay_attention_chunks(T, n_seqs)
+        work = torch.empty((chunks, n_heads, dim, vdim), dtype=torch.float32, device=rows.device)     # a state per chunk and head
+        library.check(lib.rdl_decay_attention_chunked(ctypes.byref(a), _ptr(work), work.numel() * 4, _stream(rows)), 3)
     else:
         raise KernelError(f"decay_attention: unknown kind '{kind}'")
     return out
