@@ -170,12 +170,13 @@ extern "C" int rdl_decay_attention_scan(const DecayAttentionArgs* a, void* strea
 //      in the work buffer the state BEFORE each chunk and in the cache the state after the last;
 //   3. decay_chunk_kernel<true>: a block per (chunk, head, 64 columns): P = (Q K^T) * d^(i-j) (16 rows a warp; the powers of
 //      d applied to the float sums), O = P V, and O += d^(i+1) (Q S) with the float S as two bfloat16 terms (its rounding
-//      and the remainder's), so that the state's 24 bits are not cut to 8 on the way.
+//      and the remainder's), so that the state's 24 bits are not cut to 8 on the way.  Eight warps: two share a group of
+//      16 rows and take 32 columns each, so that a block keeps twice the loads in flight while it fills shared memory.
 // The powers d^n are exp2(n log2 d) in float (d^0 = 1 also for d = 0).  Chunks are numbered over the step's sequences in
 // order; a block finds its sequence by walking the sequences' chunk counts.
 #define DC_CHUNK 64
 #define DC_COLS 64
-#define DC_THREADS 128
+#define DC_THREADS 256
 #define DC_PAD 8            // bfloat16 values between rows in shared memory: ldmatrix reads eight rows without bank conflicts
 
 __device__ __forceinline__ uint32_t dc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -400,11 +401,9 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_kernel(DecayAttentionA
     __syncthreads();
 
     if (!OUTPUT) {
-        // ---- U = K^T V_d: rows 16 (warp + 4 mi) .. + 15 of the state are this warp's ----
-#pragma unroll
-        for (int mi = 0; mi < 2; ++mi) {
-            if (warp + 4 * mi >= n_mt) continue;
-            const int m0 = (warp + 4 * mi) * 16;
+        // ---- U = K^T V_d: rows 16 warp .. + 15 of the state are this warp's ----
+        if (warp < n_mt) {
+            const int m0 = warp * 16;
             float u[8][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) u[nt][0] = u[nt][1] = u[nt][2] = u[nt][3] = 0.f;
@@ -433,17 +432,19 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_kernel(DecayAttentionA
     }
 
     // ---- P = (Q K^T) d^(i-j), rows 16 warp .. + 15 ----
-    const int i_hi = warp * 16 + g + 8;     // this thread's rows of the chunk: i_hi - 8 and i_hi
+    // warps rw and rw + 4 share the rows 16 rw .. + 15 (each forms P for itself) and take 32 of the block's 64 columns each
+    const int rw = warp & 3, cw = warp >> 2;
+    const int i_hi = rw * 16 + g + 8;       // this thread's rows of the chunk: i_hi - 8 and i_hi
     uint32_t qf[8][4];
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk)
-        if (kk < ksteps) dc_ldm4(qf[kk], dc_smem(Qs + (warp * 16 + (lane & 15)) * qs + kk * 16 + 8 * (lane >> 4)));
+        if (kk < ksteps) dc_ldm4(qf[kk], dc_smem(Qs + (rw * 16 + (lane & 15)) * qs + kk * 16 + 8 * (lane >> 4)));
     float p[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) p[nt][0] = p[nt][1] = p[nt][2] = p[nt][3] = 0.f;
 #pragma unroll
     for (int np = 0; np < 4; ++np) {
-        if (np > warp) continue;          // keys after this warp's last row
+        if (np > rw) continue;            // keys after this warp's last row
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
             if (kk >= ksteps) continue;
@@ -462,48 +463,51 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_kernel(DecayAttentionA
         }
     }
     // ---- O = P V + d^(i+1) Q S ----
-    float o[8][4], o2[8][4];
+    float o[4][4], o2[4][4];          // column tiles 4 cw .. 4 cw + 3 of the block
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; o2[nt][0] = o2[nt][1] = o2[nt][2] = o2[nt][3] = 0.f; }
+    for (int nt = 0; nt < 4; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; o2[nt][0] = o2[nt][1] = o2[nt][2] = o2[nt][3] = 0.f; }
 #pragma unroll
     for (int kb = 0; kb < 4; ++kb) {
-        if (kb > warp) continue;
+        if (kb > rw) continue;
         uint32_t pa[4] = {dc_pack(p[2 * kb][0], p[2 * kb][1]), dc_pack(p[2 * kb][2], p[2 * kb][3]),
                           dc_pack(p[2 * kb + 1][0], p[2 * kb + 1][1]), dc_pack(p[2 * kb + 1][2], p[2 * kb + 1][3])};
 #pragma unroll
-        for (int nb = 0; nb < 4; ++nb) {
+        for (int nl = 0; nl < 2; ++nl) {
+            const int nb = 2 * cw + nl;
             if (2 * nb >= nt_count) continue;
             uint32_t bf[4];
             dc_ldm4t(bf, dc_smem(Vs + (kb * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * vs + nb * 16 + ((lane >> 4) << 3)));
-            dc_mma(o[2 * nb], pa, bf[0], bf[1]);
-            dc_mma(o[2 * nb + 1], pa, bf[2], bf[3]);
+            dc_mma(o[2 * nl], pa, bf[0], bf[1]);
+            dc_mma(o[2 * nl + 1], pa, bf[2], bf[3]);
         }
     }
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
         if (kk >= ksteps) continue;
 #pragma unroll
-        for (int nb = 0; nb < 4; ++nb) {
+        for (int nl = 0; nl < 2; ++nl) {
+            const int nb = 2 * cw + nl;
             if (2 * nb >= nt_count) continue;
             const int off = (kk * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * vs + nb * 16 + ((lane >> 4) << 3);
             uint32_t bh[4], bl[4];
             dc_ldm4t(bh, dc_smem(Sh + off));
             dc_ldm4t(bl, dc_smem(Sl + off));
-            dc_mma(o2[2 * nb], qf[kk], bh[0], bh[1]);
-            dc_mma(o2[2 * nb + 1], qf[kk], bh[2], bh[3]);
-            dc_mma(o2[2 * nb], qf[kk], bl[0], bl[1]);
-            dc_mma(o2[2 * nb + 1], qf[kk], bl[2], bl[3]);
+            dc_mma(o2[2 * nl], qf[kk], bh[0], bh[1]);
+            dc_mma(o2[2 * nl + 1], qf[kk], bh[2], bh[3]);
+            dc_mma(o2[2 * nl], qf[kk], bl[0], bl[1]);
+            dc_mma(o2[2 * nl + 1], qf[kk], bl[2], bl[3]);
         }
     }
     const float w_lo = pw[i_hi - 8 + 1], w_hi = pw[i_hi + 1];
     float* out_lo = a.out + (long long)(row0 + t0 + i_hi - 8) * a.n_heads * vdim + (long long)h * vdim + c0;
     float* out_hi = out_lo + 8LL * a.n_heads * vdim;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nl = 0; nl < 4; ++nl) {
+        const int nt = 4 * cw + nl;
         if (nt >= nt_count) continue;
         const int c = nt * 8 + 2 * tq;
-        if (i_hi - 8 < L) *reinterpret_cast<float2*>(out_lo + c) = make_float2(fmaf(w_lo, o2[nt][0], o[nt][0]), fmaf(w_lo, o2[nt][1], o[nt][1]));
-        if (i_hi < L) *reinterpret_cast<float2*>(out_hi + c) = make_float2(fmaf(w_hi, o2[nt][2], o[nt][2]), fmaf(w_hi, o2[nt][3], o[nt][3]));
+        if (i_hi - 8 < L) *reinterpret_cast<float2*>(out_lo + c) = make_float2(fmaf(w_lo, o2[nl][0], o[nl][0]), fmaf(w_lo, o2[nl][1], o[nl][1]));
+        if (i_hi < L) *reinterpret_cast<float2*>(out_hi + c) = make_float2(fmaf(w_hi, o2[nl][2], o[nl][2]), fmaf(w_hi, o2[nl][3], o[nl][3]));
     }
 }
 
