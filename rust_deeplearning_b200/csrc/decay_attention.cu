@@ -511,7 +511,7 @@ __global__ void __launch_bounds__(DC_THREADS) decay_chunk_kernel(DecayAttentionA
     }
 }
 
-// S' = d^L S + U over a sequence's chunks, a thread per state element; the work buffer keeps the state before each chunk
+// S' = d^L S + U over a sequence's chunks, a thread per four state elements; the work buffer keeps the state before each chunk
 __global__ void __launch_bounds__(256) decay_chunk_scan_kernel(DecayAttentionArgs a, float* __restrict__ work) {
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -523,30 +523,35 @@ __global__ void __launch_bounds__(256) decay_chunk_scan_kernel(DecayAttentionArg
         const int m = a.seq_start[s + 1] - a.seq_start[s];
         if (m > 0 && a.tok_pos[a.seq_start[s]] >= 0) first += (m + DC_CHUNK - 1) / DC_CHUNK;
     }
-    const long long per = (long long)a.dim * a.vdim;
-    const long long e = (long long)blockIdx.z * blockDim.x + threadIdx.x;
+    const long long per = (long long)a.dim * a.vdim;          // a multiple of 4 (both sizes are multiples of 16)
+    const long long e = 4 * ((long long)blockIdx.z * blockDim.x + threadIdx.x);
     if (e >= per) return;
     const float decay = a.decay[h];
     const float full = decay > 0.f ? exp2f((float)DC_CHUNK * log2f(decay)) : 0.f;
-    float* S = a.state + ((long long)a.slots[seq] * a.n_heads + h) * per + e;
-    float s = *S;
+    float4* S = reinterpret_cast<float4*>(a.state + ((long long)a.slots[seq] * a.n_heads + h) * per + e);
+    float4 s = *S;
     const int chunks = (n + DC_CHUNK - 1) / DC_CHUNK;
-    float* w = work + ((long long)first * a.n_heads + h) * per + e;
-    const long long step = (long long)a.n_heads * per;
-    for (int c = 0; c < chunks; c += 8) {        // eight chunks' values asked for before the first is used
-        float u[8];
+    float4* w = reinterpret_cast<float4*>(work + ((long long)first * a.n_heads + h) * per + e);
+    const long long step = (long long)a.n_heads * per / 4;
+    // four chunks' values are asked for while the four before them are summed and stored: loads stay in flight throughout
+    float4 u[4], nx[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) u[i] = c + i < chunks ? __ldcg(w + i * step) : 0.f;
+    for (int i = 0; i < 4; ++i) u[i] = i < chunks ? __ldcg(w + i * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < chunks; c += 4) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) nx[i] = c + 4 + i < chunks ? __ldcg(w + (4 + i) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
             if (c + i < chunks) {
                 __stcg(w + i * step, s);
                 const int L = min(DC_CHUNK, n - (c + i) * DC_CHUNK);
                 const float dl = L == DC_CHUNK ? full : (decay > 0.f ? exp2f((float)L * log2f(decay)) : 0.f);
-                s = fmaf(dl, s, u[i]);
+                s.x = fmaf(dl, s.x, u[i].x); s.y = fmaf(dl, s.y, u[i].y); s.z = fmaf(dl, s.z, u[i].z); s.w = fmaf(dl, s.w, u[i].w);
             }
         }
-        w += 8 * step;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) u[i] = nx[i];
+        w += 4 * step;
     }
     *S = s;
 }
@@ -556,8 +561,8 @@ extern "C" int rdl_decay_attention_chunked(const DecayAttentionArgs* a, void* wo
     RDL_REQUIRE(a->dtype == RDL_BF16, "decay_attention_chunked: bfloat16 rows only");
     RDL_REQUIRE(a->dim % 16 == 0 && a->dim <= 128 && a->vdim % 16 == 0, "decay_attention_chunked: dim %d and vdim %d must be multiples of 16, dim at most 128",
                 a->dim, a->vdim);
-    RDL_REQUIRE(((uintptr_t)a->out & 7) == 0 && ((uintptr_t)a->state & 7) == 0 && ((uintptr_t)work & 7) == 0,
-                "decay_attention_chunked: output, state and work buffer must be 8-byte aligned");
+    RDL_REQUIRE(((uintptr_t)a->out & 7) == 0 && ((uintptr_t)a->state & 15) == 0 && ((uintptr_t)work & 15) == 0,
+                "decay_attention_chunked: the output must be 8-byte aligned, state and work buffer 16-byte aligned");
     RDL_REQUIRE((a->v_col % 2) == 0 && (a->row_stride % 2) == 0 && ((uintptr_t)a->rows & 3) == 0,
                 "decay_attention_chunked: the value heads must start at an even column of 4-byte aligned rows");
     if (a->n_tokens == 0 || a->n_seqs == 0) return 0;
@@ -579,7 +584,7 @@ extern "C" int rdl_decay_attention_chunked(const DecayAttentionArgs* a, void* wo
                     (a->rot_n / 2) % 8 == 0 && (a->rot_n == 0 || ((((uintptr_t)a->cos_t) | ((uintptr_t)a->sin_t)) & 15) == 0);
     RDL_CHECK_EX(rdl_launch(decay_chunk_kernel<false>, grid, dim3(DC_THREADS), smem_u, st, *a, (float*)work, vec), "decay_attention_chunked (chunk states)");
     const long long per = (long long)a->dim * a->vdim;
-    RDL_CHECK_EX(rdl_launch(decay_chunk_scan_kernel, dim3(a->n_seqs, a->n_heads, (unsigned)((per + 255) / 256)), dim3(256), 0, st, *a, (float*)work),
+    RDL_CHECK_EX(rdl_launch(decay_chunk_scan_kernel, dim3(a->n_seqs, a->n_heads, (unsigned)((per / 4 + 127) / 128)), dim3(128), 0, st, *a, (float*)work),
                  "decay_attention_chunked (scan)");
     RDL_CHECK_EX(rdl_launch(decay_chunk_kernel<true>, grid, dim3(DC_THREADS), smem_o, st, *a, (float*)work, vec), "decay_attention_chunked (outputs)");
     return 0;

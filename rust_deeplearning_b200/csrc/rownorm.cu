@@ -10,6 +10,13 @@ __device__ __forceinline__ float gate_value(float g, int act) {
     return act == RDL_GATE_SILU ? g * s : s;
 }
 
+// For results that are rounded to bfloat16 anyway: the hardware's exponential and reciprocal (a few units in the last
+// place of a float, far below a bfloat16's half unit).
+__device__ __forceinline__ float gate_value_fast(float g, int act) {
+    const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+    return act == RDL_GATE_SILU ? g * s : s;
+}
+
 // Four consecutive values at a time, and a row (or group) held in registers between its two passes: every load of a
 // thread is asked for before the first is used, so a row costs one trip to memory however wide it is.  Used when
 // the width is a multiple of 4 and a thread's share fits RN_MAX_IT groups of four; the plain loops further down serve the rest.
@@ -44,8 +51,15 @@ static inline int vec_threads(int width) {
 }
 static inline bool vec_ok(int width, int threads) { return width % 4 == 0 && (width / 4 + threads - 1) / threads <= RN_MAX_IT; }
 static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+// groups of four a thread takes, rounded up to 1, 2, 4 or 8 (the kernels' unrolled depth)
+static inline int vec_depth(int width, int threads) {
+    const int need = (width / 4 + threads - 1) / threads;
+    return need <= 1 ? 1 : (need <= 2 ? 2 : (need <= 4 ? 4 : 8));
+}
+#define RN_BY_DEPTH(depth, LAUNCH) \
+    switch (depth) { case 1: LAUNCH(1); break; case 2: LAUNCH(2); break; case 4: LAUNCH(4); break; default: LAUNCH(8); break; }
 
-template <typename TB, typename TY>
+template <typename TB, typename TY, int NIT>
 __global__ void __launch_bounds__(256) postnorm_vec_kernel(float* __restrict__ res, const TB* __restrict__ branch, float alpha,
                                                            const void* __restrict__ w, int w_dtype, float eps, float off,
                                                            TY* __restrict__ y, int width) {
@@ -54,15 +68,15 @@ __global__ void __launch_bounds__(256) postnorm_vec_kernel(float* __restrict__ r
     rdl_grid_launch_dependents();
     float* r = res + (long long)blockIdx.x * width;
     const TB* b = branch + (long long)blockIdx.x * width;
-    float h[RN_MAX_IT][4], bv[RN_MAX_IT][4];
+    float h[NIT][4], bv[NIT][4];
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (threadIdx.x + it * blockDim.x) * 4;
         if (e < width) { rn_load4(r + e, h[it]); rn_load4(b + e, bv[it]); }
     }
     float ss = 0.f;
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (threadIdx.x + it * blockDim.x) * 4;
         if (e < width) {
 #pragma unroll
@@ -72,7 +86,7 @@ __global__ void __launch_bounds__(256) postnorm_vec_kernel(float* __restrict__ r
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (threadIdx.x + it * blockDim.x) * 4;
         if (e < width) {
             float wv[4], v[4];
@@ -85,7 +99,7 @@ __global__ void __launch_bounds__(256) postnorm_vec_kernel(float* __restrict__ r
     }
 }
 
-template <typename T>
+template <typename T, int NIT>
 __global__ void __launch_bounds__(256) norm_pair_vec_kernel(float* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
                                                             const void* __restrict__ wa, const void* __restrict__ wb, int w_dtype,
                                                             float eps, float c, int width) {
@@ -94,15 +108,15 @@ __global__ void __launch_bounds__(256) norm_pair_vec_kernel(float* __restrict__ 
     rdl_grid_launch_dependents();
     const T* ra = a + (long long)blockIdx.x * width;
     const T* rb = b + (long long)blockIdx.x * width;
-    float x[RN_MAX_IT][4], z[RN_MAX_IT][4];
+    float x[NIT][4], z[NIT][4];
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (threadIdx.x + it * blockDim.x) * 4;
         if (e < width) { rn_load4(ra + e, x[it]); rn_load4(rb + e, z[it]); }
     }
     float sa = 0.f, sb = 0.f;
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (threadIdx.x + it * blockDim.x) * 4;
         if (e < width) {
 #pragma unroll
@@ -113,7 +127,7 @@ __global__ void __launch_bounds__(256) norm_pair_vec_kernel(float* __restrict__ 
     sb = block_sum(sb, scratch);
     const float ia = 1.0f / sqrtf(sa / (float)width + eps), ib = 1.0f / sqrtf(sb / (float)width + eps);
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (threadIdx.x + it * blockDim.x) * 4;
         if (e < width) {
             float va[4], vb[4], v[4];
@@ -127,7 +141,7 @@ __global__ void __launch_bounds__(256) norm_pair_vec_kernel(float* __restrict__ 
 }
 
 // a warp per group (groups of up to 1,024 values), or a block per group (WARP false)
-template <typename TO, bool WARP>
+template <typename TO, bool WARP, int NIT>
 __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, long long n_items, int groups,
                                                                   int group, const void* __restrict__ w, int w_dtype, float eps,
                                                                   const void* __restrict__ g, long long g_stride, int g_dtype, int act) {
@@ -140,9 +154,9 @@ __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict
     const long long t = item / groups;
     const int gi = (int)(item - t * groups), col0 = gi * group;
     const long long base = item * group;
-    float v[RN_MAX_IT][4], gv[RN_MAX_IT][4];
+    float v[NIT][4], gv[NIT][4];
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (lane + it * stride) * 4;
         if (e < group) {
             rn_load4(x + base + e, v[it]);
@@ -151,7 +165,7 @@ __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict
     }
     float ss = 0.f;
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (lane + it * stride) * 4;
         if (e < group) {
 #pragma unroll
@@ -161,7 +175,7 @@ __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict
     ss = WARP ? warp_sum(ss) : block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)group + eps);
 #pragma unroll
-    for (int it = 0; it < RN_MAX_IT; ++it) {
+    for (int it = 0; it < NIT; ++it) {
         const int e = (lane + it * stride) * 4;
         if (e < group) {
             float o[4], wv[4];
@@ -170,7 +184,7 @@ __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict
             for (int k = 0; k < 4; ++k) {
                 o[k] = v[it][k] * inv;
                 if (w) o[k] *= wv[k];
-                if (g) o[k] *= gate_value(gv[it][k], act);
+                if (g) o[k] *= sizeof(TO) == 2 ? gate_value_fast(gv[it][k], act) : gate_value(gv[it][k], act);
             }
             rn_store4(out + base + e, o);
         }
@@ -213,21 +227,26 @@ extern "C" int rdl_postnorm(float* res, const void* branch, int branch_dtype, fl
     const int vt = vec_threads(width);
     if (vec_ok(width, vt) && aligned16(res) && aligned16(branch) && aligned16(w) && aligned16(y)) {
         const dim3 grid(n_rows), block(vt);
-        if (branch_dtype == RDL_BF16) {
-            if (y_dtype == RDL_BF16)
-                e = rdl_launch(postnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, st, res, (const __nv_bfloat16*)branch, alpha,
-                               w, w_dtype, eps, off, (__nv_bfloat16*)y, width);
-            else
-                e = rdl_launch(postnorm_vec_kernel<__nv_bfloat16, float>, grid, block, 0, st, res, (const __nv_bfloat16*)branch, alpha, w,
-                               w_dtype, eps, off, (float*)y, width);
-        } else {
-            if (y_dtype == RDL_BF16)
-                e = rdl_launch(postnorm_vec_kernel<float, __nv_bfloat16>, grid, block, 0, st, res, (const float*)branch, alpha, w, w_dtype,
-                               eps, off, (__nv_bfloat16*)y, width);
-            else
-                e = rdl_launch(postnorm_vec_kernel<float, float>, grid, block, 0, st, res, (const float*)branch, alpha, w, w_dtype, eps, off,
-                               (float*)y, width);
-        }
+#define POSTNORM_LAUNCH(N)                                                                                                          \
+    do {                                                                                                                            \
+        if (branch_dtype == RDL_BF16) {                                                                                             \
+            if (y_dtype == RDL_BF16)                                                                                                \
+                e = rdl_launch(postnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16, N>, grid, block, 0, st, res,                       \
+                               (const __nv_bfloat16*)branch, alpha, w, w_dtype, eps, off, (__nv_bfloat16*)y, width);                \
+            else                                                                                                                    \
+                e = rdl_launch(postnorm_vec_kernel<__nv_bfloat16, float, N>, grid, block, 0, st, res, (const __nv_bfloat16*)branch, \
+                               alpha, w, w_dtype, eps, off, (float*)y, width);                                                      \
+        } else {                                                                                                                    \
+            if (y_dtype == RDL_BF16)                                                                                                \
+                e = rdl_launch(postnorm_vec_kernel<float, __nv_bfloat16, N>, grid, block, 0, st, res, (const float*)branch, alpha,  \
+                               w, w_dtype, eps, off, (__nv_bfloat16*)y, width);                                                     \
+            else                                                                                                                    \
+                e = rdl_launch(postnorm_vec_kernel<float, float, N>, grid, block, 0, st, res, (const float*)branch, alpha, w,       \
+                               w_dtype, eps, off, (float*)y, width);                                                                \
+        }                                                                                                                           \
+    } while (0)
+        RN_BY_DEPTH(vec_depth(width, vt), POSTNORM_LAUNCH)
+#undef POSTNORM_LAUNCH
         RDL_CHECK_EX(e, "postnorm");
         return 0;
     }
@@ -285,12 +304,17 @@ extern "C" int rdl_norm_pair(float* out, const void* a, const void* b, int dtype
     cudaError_t e;
     const int vt = vec_threads(width);
     if (vec_ok(width, vt) && aligned16(out) && aligned16(a) && aligned16(b) && aligned16(wa) && aligned16(wb)) {
-        if (dtype == RDL_BF16)
-            e = rdl_launch(norm_pair_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vt), 0, st, out, (const __nv_bfloat16*)a,
-                           (const __nv_bfloat16*)b, wa, wb, w_dtype, eps, c, width);
-        else
-            e = rdl_launch(norm_pair_vec_kernel<float>, dim3(n_rows), dim3(vt), 0, st, out, (const float*)a, (const float*)b, wa, wb,
-                           w_dtype, eps, c, width);
+#define NORM_PAIR_LAUNCH(N)                                                                                                  \
+    do {                                                                                                                     \
+        if (dtype == RDL_BF16)                                                                                               \
+            e = rdl_launch(norm_pair_vec_kernel<__nv_bfloat16, N>, dim3(n_rows), dim3(vt), 0, st, out, (const __nv_bfloat16*)a, \
+                           (const __nv_bfloat16*)b, wa, wb, w_dtype, eps, c, width);                                         \
+        else                                                                                                                 \
+            e = rdl_launch(norm_pair_vec_kernel<float, N>, dim3(n_rows), dim3(vt), 0, st, out, (const float*)a, (const float*)b, \
+                           wa, wb, w_dtype, eps, c, width);                                                                  \
+    } while (0)
+        RN_BY_DEPTH(vec_depth(width, vt), NORM_PAIR_LAUNCH)
+#undef NORM_PAIR_LAUNCH
         RDL_CHECK_EX(e, "norm_pair");
         return 0;
     }
@@ -380,13 +404,22 @@ extern "C" int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int
         const int vt = vec_threads(group);
         if (warp || vec_ok(group, vt)) {
             const dim3 grid(warp ? (unsigned)((n_items + 7) / 8) : (unsigned)n_items), block(warp ? 256 : vt);
-            if (out_dtype == RDL_BF16) {
-                if (warp) e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, true>, grid, block, 0, st, (__nv_bfloat16*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
-                else e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, false>, grid, block, 0, st, (__nv_bfloat16*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
-            } else {
-                if (warp) e = rdl_launch(group_norm_gate_vec_kernel<float, true>, grid, block, 0, st, (float*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
-                else e = rdl_launch(group_norm_gate_vec_kernel<float, false>, grid, block, 0, st, (float*)out, x, n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);
-            }
+#define GROUP_NORM_LAUNCH(N)                                                                                                             \
+    do {                                                                                                                                 \
+        if (out_dtype == RDL_BF16) {                                                                                                     \
+            if (warp) e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, true, N>, grid, block, 0, st, (__nv_bfloat16*)out, x,     \
+                                     n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                           \
+            else e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, false, N>, grid, block, 0, st, (__nv_bfloat16*)out, x,         \
+                                n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                                \
+        } else {                                                                                                                         \
+            if (warp) e = rdl_launch(group_norm_gate_vec_kernel<float, true, N>, grid, block, 0, st, (float*)out, x, n_items, groups,    \
+                                     group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                                            \
+            else e = rdl_launch(group_norm_gate_vec_kernel<float, false, N>, grid, block, 0, st, (float*)out, x, n_items, groups, group, \
+                                w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                                                        \
+        }                                                                                                                                \
+    } while (0)
+            RN_BY_DEPTH(vec_depth(group, warp ? 32 : vt), GROUP_NORM_LAUNCH)
+#undef GROUP_NORM_LAUNCH
             RDL_CHECK_EX(e, "group_norm_gate");
             return 0;
         }
