@@ -342,6 +342,30 @@ __global__ void gate_mul_kernel(T* __restrict__ out, long long out_stride, const
     }
 }
 
+// the same, eight bfloat16 values (16 bytes) a thread; width and the three strides are multiples of 8
+__global__ void gate_mul_vec_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ x, long long x_stride,
+                                    const __nv_bfloat16* __restrict__ g, long long g_stride, int act, int n_rows, int width) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int per_row = width >> 3;
+    const long long total = (long long)n_rows * per_row;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / per_row;
+        const int i = (int)(idx - t * per_row) << 3;
+        const uint4 xr = *reinterpret_cast<const uint4*>(x + t * x_stride + i), gr = *reinterpret_cast<const uint4*>(g + t * g_stride + i);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xr);
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gr);
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 xv = __bfloat1622float2(xp[k]), gv = __bfloat1622float2(gp[k]);
+            op[k] = __floats2bfloat162_rn(xv.x * gate_value_fast(gv.x, act), xv.y * gate_value_fast(gv.y, act));
+        }
+        *reinterpret_cast<uint4*>(out + t * out_stride + i) = o;
+    }
+}
+
 extern "C" int rdl_gate_mul(void* out, long long out_stride, const void* x, long long x_stride, const void* g, long long g_stride,
                             int dtype, int gate_act, int n_rows, int width, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "gate_mul: bad dtype %d", dtype);
@@ -353,6 +377,15 @@ extern "C" int rdl_gate_mul(void* out, long long out_stride, const void* x, long
     const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
+    if (dtype == RDL_BF16 && width % 8 == 0 && out_stride % 8 == 0 && x_stride % 8 == 0 && g_stride % 8 == 0 && aligned16(out) &&
+        aligned16(x) && aligned16(g)) {
+        const long long groups = total / 8;
+        const unsigned vblocks = (unsigned)((groups + 255) / 256 < 65535 * 8 ? (groups + 255) / 256 : 65535 * 8);
+        e = rdl_launch(gate_mul_vec_kernel, dim3(vblocks), dim3(256), 0, st, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)x, x_stride,
+                       (const __nv_bfloat16*)g, g_stride, gate_act, n_rows, width);
+        RDL_CHECK_EX(e, "gate_mul");
+        return 0;
+    }
     if (dtype == RDL_BF16)
         e = rdl_launch(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st, (__nv_bfloat16*)out, out_stride,
                        (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)g, g_stride, gate_act, n_rows, width);
