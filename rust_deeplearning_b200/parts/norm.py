@@ -13,6 +13,10 @@ the branch, add it to the stream, norm the sum for the next part" is ONE kernel
 that reads the branch and the stream once.  Any other norm kind (anything with an
 `apply`) takes the same route through separate kernels.
 
+For blocks that norm AFTER the sum the stream offers `rows(dtype)` (the stream itself as a part's input) and
+`renorm(branch, norm, alpha, dtype)`: x <- norm(alpha x + branch) in float32, in place, in one kernel that also
+leaves x in the activations' dtype for the next part.
+
 Interface of a norm: `apply(x [rows, hidden], out_dtype) -> [rows, hidden]`;
 optionally `fused_params() -> ops.NormParams`.
 """

@@ -126,6 +126,19 @@ def test_attention_with_sinks(kind, dtype, head_dim):
              dtype=dtype, seed=41)
     sinks = torch.tensor([-30.0, -1.0, 0.0, 0.7, 3.0, 12.0], dtype=torch.float32, device=DEV)
     b = c.batch("all" if decode else "past")
+    # one key far back (position 2 of the longest sequence) is made to stand out for that sequence's last query: random
+    # keys would hide a kernel that loses the oldest page or the first key tile
+    s_far = int(np.argmax([p + n for p, n in zip(past, new)]))
+    last_row = int(c.seq_start[s_far + 1]) - 1
+    for g in range(2):
+        qv = c.qkv[last_row, g * 3 * head_dim:(g * 3 + 1) * head_dim].float()
+        kv = (qv / qv.norm() * 12.0).to(dtype)
+        if past[s_far] > 2:
+            page, r = ref._cache_index(c.pages.tables[s_far].cpu(), 2, c.page_size, c.ring_pages)
+            ref.cache_store(c.pages.k[page, g, r], kv, r)
+        else:
+            row = int(c.seq_start[s_far]) + 2
+            c.qkv[row, (6 + g) * head_dim:(7 + g) * head_dim] = kv
     if decode:       # the step's own rows are in the cache already
         ref.rope_cache(c.qkv, 6, 2, head_dim, tok_seq=c.tok_seq, tok_pos=c.tok_pos, pages=c.pages, seq_end=c.seq_end)
     for softcap in (None, 4.0):
