@@ -296,6 +296,95 @@ __global__ void rope_norm_cache_kernel(T* __restrict__ rows, long long row_strid
     }
 }
 
+// The same with 16-byte accesses, for heads and rotated halves that are whole numbers of 16-byte chunks.  A head is taken
+// by a group of LPH lanes (a power of two; 32 / LPH heads a warp at a time): a lane holds one rotated pair of chunks, or one
+// chunk of the part that does not rotate, in registers; the squares are summed across the group in a fixed order; every
+// value is loaded once and stored once.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_norm_cache_vec_kernel(T* __restrict__ rows, long long row_stride, int n_heads, int n_kv_heads,
+                                                                  int head_dim, int rotary_dim, const float* __restrict__ cos_t,
+                                                                  const float* __restrict__ sin_t, const int* __restrict__ tok_seq,
+                                                                  const int* __restrict__ tok_pos, int do_rope, float norm_eps, int norm_dim,
+                                                                  int do_write, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                                  const int* __restrict__ tables, int table_width, int page_size,
+                                                                  int ring_pages, const int* __restrict__ seq_end, int lph) {
+    constexpr int N = Chunk<T>::N;
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    if (pos < 0) return;  // a padding row of a fixed-size batch
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int per_warp = 32 / lph, sub = lane / lph, li = lane - sub * lph;
+    const int chunks = head_dim / N, half = do_rope ? rotary_dim >> 1 : 0, hc = half / N;
+    const int items = chunks - hc;                 // pairs, then single chunks
+    bool write = do_write && n_kv_heads > 0;
+    const int seq = tok_seq[t];
+    // In a ring a later token of this step may land on the same row: only the last writer writes.
+    if (write && (long long)pos + (long long)ring_pages * page_size < (long long)seq_end[seq]) write = false;
+    const int r = pos % page_size;
+    const int total = n_heads + 2 * n_kv_heads;
+    for (int h0 = warp * per_warp; h0 < total; h0 += n_warps * per_warp) {     // the same trips for every lane of a warp
+        const int head = h0 + sub;
+        const bool live = head < total;
+        const bool is_q = head < n_heads, is_v = head >= n_heads + n_kv_heads;
+        T* row = rows + (long long)t * row_stride + (long long)(live ? head : 0) * head_dim;
+        T* dst = nullptr;
+        if (live && write && !is_q) {
+            const int kv_head = is_v ? head - n_heads - n_kv_heads : head - n_heads;
+            dst = (is_v ? v_cache : k_cache) +
+                  rdl_cache_offset(tables + (long long)seq * table_width, pos, page_size, ring_pages, n_kv_heads, kv_head, head_dim);
+        }
+        if (live && is_v) {
+            if (dst)
+                for (int c = li; c < chunks; c += lph)
+                    *reinterpret_cast<uint4*>(dst + rdl_swizzled_chunk(r, c, chunks) * N) = *reinterpret_cast<const uint4*>(row + c * N);
+        }
+        const bool mine = live && !is_v && li < items;
+        const bool pair = mine && li < hc;
+        const int c_lo = pair ? li : li + hc;      // the chunk this lane holds (and, for a pair, c_lo + hc)
+        float a[N], b[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) a[i] = b[i] = 0.f;
+        if (mine) Chunk<T>::load(row + c_lo * N, a);
+        if (pair) {
+            Chunk<T>::load(row + (c_lo + hc) * N, b);
+            float cs[N], sn[N];
+            const float4* cp = reinterpret_cast<const float4*>(cos_t + (long long)pos * half + c_lo * N);
+            const float4* sp = reinterpret_cast<const float4*>(sin_t + (long long)pos * half + c_lo * N);
+#pragma unroll
+            for (int i = 0; i < N / 4; ++i) {
+                const float4 cv = __ldg(cp + i), sv = __ldg(sp + i);
+                cs[4 * i] = cv.x; cs[4 * i + 1] = cv.y; cs[4 * i + 2] = cv.z; cs[4 * i + 3] = cv.w;
+                sn[4 * i] = sv.x; sn[4 * i + 1] = sv.y; sn[4 * i + 2] = sv.z; sn[4 * i + 3] = sv.w;
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const float lo = a[i] * cs[i] - b[i] * sn[i], hi = b[i] * cs[i] + a[i] * sn[i];
+                a[i] = lo;
+                b[i] = hi;
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < N; ++i) { ss = fmaf(a[i], a[i], ss); ss = fmaf(b[i], b[i], ss); }
+        for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = norm_eps > 0.f ? 1.0f / sqrtf(ss / (float)norm_dim + norm_eps) : 1.0f;
+        if (mine) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) { a[i] *= inv; b[i] *= inv; }
+            const uint4 pa = Chunk<T>::pack(a);
+            *reinterpret_cast<uint4*>(row + c_lo * N) = pa;
+            if (dst) *reinterpret_cast<uint4*>(dst + rdl_swizzled_chunk(r, c_lo, chunks) * N) = pa;
+            if (pair) {
+                const uint4 pb = Chunk<T>::pack(b);
+                *reinterpret_cast<uint4*>(row + (c_lo + hc) * N) = pb;
+                if (dst) *reinterpret_cast<uint4*>(dst + rdl_swizzled_chunk(r, c_lo + hc, chunks) * N) = pb;
+            }
+        }
+    }
+}
+
 extern "C" int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                    int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq,
                                    const int* tok_pos, int do_rope, float norm_eps, int norm_dim, int do_write, void* k_cache,
@@ -313,14 +402,37 @@ extern "C" int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, 
                     (k_cache && v_cache && tables && seq_end && page_size > 0 && ring_pages > 0 && ring_pages <= table_width),
                 "rope_norm_cache: cache write needs storage, page tables and lengths");
     if (n_tokens == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    {
+        const int per_chunk = dtype == RDL_BF16 ? 8 : 4;
+        const int half = do_rope ? rotary_dim / 2 : 0;
+        const bool aligned = (((uintptr_t)rows | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_table | (uintptr_t)sin_table) & 15) == 0;
+        const int items = head_dim % per_chunk == 0 && half % per_chunk == 0 ? head_dim / per_chunk - half / per_chunk : 0;
+        if (aligned && items > 0 && items <= 32 && row_stride % per_chunk == 0) {
+            int lph = 1;
+            while (lph < items) lph *= 2;
+            const int per_warp = 32 / lph, total = n_heads + 2 * n_kv_heads;
+            int warps = (total + per_warp - 1) / per_warp;
+            warps = warps > 8 ? 8 : warps;
+            if (dtype == RDL_BF16)
+                e = rdl_launch(rope_norm_cache_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(warps * 32), 0, st, (__nv_bfloat16*)rows, row_stride,
+                               n_heads, n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, norm_eps, norm_dim,
+                               do_write, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tables, table_width, page_size, ring_pages, seq_end, lph);
+            else
+                e = rdl_launch(rope_norm_cache_vec_kernel<float>, dim3(n_tokens), dim3(warps * 32), 0, st, (float*)rows, row_stride, n_heads,
+                               n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, norm_eps, norm_dim, do_write,
+                               (float*)k_cache, (float*)v_cache, tables, table_width, page_size, ring_pages, seq_end, lph);
+            RDL_CHECK_EX(e, "rope_norm_cache");
+            return 0;
+        }
+    }
     // a warp per head while a block's shared memory and thread count allow it: a head is three dependent steps
     // (load and rotate, sum, scale and store), so heads one after another in a warp are trips to memory one after another
     int warps = n_heads + 2 * n_kv_heads;
     if (warps > 16) warps = 16;
     while (warps > 1 && (size_t)warps * head_dim * sizeof(float) > 40 * 1024) warps /= 2;
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
-    cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e;
     if (dtype == RDL_BF16)
         e = rdl_launch(rope_norm_cache_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(warps * 32), smem, st, (__nv_bfloat16*)rows, row_stride,
                        n_heads, n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, norm_eps, norm_dim,
