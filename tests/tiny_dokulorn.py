@@ -52,7 +52,7 @@ DC = {
     "architecture": "Dokulorn", "width": 128, "vocab": 300, "norm": {"eps": 1e-6}, "postln_alpha": 3.0, "embedding": {"scale": 7.5},
     "max_positions": 2048,
     "layers": [
-        {"type": "retention", "mixer": _ret(2, 64, 128, [0.98, 0.9995], _rot(1e6, 64)), "mlp": None},
+        {"type": "retention", "mixer": _ret(2, 64, 128, [0.98, 0.9995], _rot(5e5, 64)), "mlp": None},
         {"type": "parallel", "mixer": {"left": _left(4, 1, 64, 64, _rot(10000.0, 32), 1.1, 15.0), "right": _right(2, 128, 32, [0.0, 0.96])},
          "mlp": {"kind": "dense", "ff": 192}},
         {"type": "retention", "mixer": _ret(1, 128, 64, [0.999], _rot(777.0, 128)), "mlp": None},
